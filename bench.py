@@ -1,0 +1,426 @@
+#!/usr/bin/env python
+"""Benchmark of the Q4_K x Q8 decode hot path (and, as extra keys, of the prefill path).
+
+Workload at every N: one hybrid-layer decode projection set (QKV 7168x5120, O 5120x5120,
+gate+up 34816x5120, down 5120x17408, Q4_K weights, bf16 N(0,1) activations quantised on the
+device) at M in {1,2,4,8,16}.  One step = the five token counts over one layer copy each;
+weights rotate over LAYERS distinct copies (>126 MB L2) so HBM serves them.  With N>1 GPUs
+every matrix is split by output rows over the ranks and the output slices are all-gathered.
+
+Prints ONE JSON line (rank 0).  `--impl reference` times the CPU restatement of the reference
+equation on the host cores instead (rank 0 only)."""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+SHAPES = [("qkv", 7168, 5120), ("o", 5120, 5120), ("gate_up", 34816, 5120), ("down", 5120, 17408)]
+TOKENS = [1, 2, 4, 8, 16]
+LAYERS = 8
+METRIC = "q4k_q8_decode_projection_set_GBps"
+
+
+def weight_bytes(n, k):
+    return n * (k // 256) * 144
+
+
+def algorithmic_bytes(m, n, k, with_quantise=True):
+    """Q4_K weights read once + Q8 activations (codes, fp32 scale, int32 sum) + fp32 output
+    (+ the bf16 rows when the quantiser runs inside the timed region)."""
+    b = weight_bytes(n, k) + m * (k + (k // 32) * 8) + m * n * 4
+    return b + (m * k * 2 if with_quantise else 0)
+
+
+def step_bytes():
+    total = 0
+    for m in TOKENS:
+        for _, n, k in SHAPES:
+            total += algorithmic_bytes(m, n, k, with_quantise=False)
+        total += m * 5120 * 2 + m * 17408 * 2  # two bf16 inputs quantised per token count
+    return total
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.lines, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append((time.time(), line.strip()))
+
+    def stop(self, t0: float, t1: float) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        rows = [l for (t, l) in self.lines if t0 - 0.05 <= t <= t1 + 0.15] or [l for (_, l) in self.lines]
+        sm, smax, reasons = [], [], set()
+        for l in rows:
+            f = [x.strip() for x in l.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"], f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------------------------
+# CPU arm: the oracle port of the reference equation on the host cores
+# ----------------------------------------------------------------------------------------------
+def cpu_sample(repeats: int, rows_per_matrix: int = 256):
+    """Times the CPU restatement on a bounded sample: `rows_per_matrix` output rows of every
+    matrix of the set, all five token counts, all host cores.  Returns (GB/s, cores, text)."""
+    from oracle import oracle as orc
+    from qw38_b200 import synth
+    handle = orc.lib(native=True)
+    cores = handle.orc_num_threads()
+    mats = []
+    for i, (_, n, k) in enumerate(SHAPES):
+        codes, meta = synth.logical_q4k(rows_per_matrix, k, seed=100 + i)
+        mats.append((k,) + synth.split_tiles(codes, meta))
+    acts = {}
+    for m in TOKENS:
+        for k in (5120, 17408):
+            xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=m))
+            acts[(m, k)] = orc.q8_quantize(xb, bf16_bits=True)[:3]
+    nbytes = sum(algorithmic_bytes(m, rows_per_matrix, k, with_quantise=False) for m in TOKENS for _, _, k in SHAPES)
+    best = float("inf")
+    for _ in range(max(1, repeats)):
+        t0 = time.perf_counter()
+        for m in TOKENS:
+            for (k, hc, hs) in mats:
+                z, a, s = acts[(m, k)]
+                orc.project_rows(hc, hs, rows_per_matrix, k, z, a, s, 0, rows_per_matrix, handle=handle)
+        best = min(best, time.perf_counter() - t0)
+    return nbytes / best / 1e9, cores, f"{rows_per_matrix} rows of each of the 4 matrices, M in {TOKENS}, best of {max(1, repeats)}"
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps, warm = max(1, args.steps), max(0, args.warmup)
+    cpu_sample(1)  # build + warm caches
+    for _ in range(warm):
+        cpu_sample(1)
+    t0 = time.perf_counter()
+    vals = [cpu_sample(1) for _ in range(steps)]
+    elapsed = time.perf_counter() - t0
+    gbps = statistics.median(v[0] for v in vals)
+    cores, sample = vals[0][1], vals[0][2]
+    line = {"impl": "reference", "metric": METRIC, "value": gbps, "unit": "GB/s", "n_gpus": args.gpus,
+            "steps": steps, "warmup": warm, "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot / fp32 affine", "data": "synthetic",
+            "config": {"workload": "config[1] decode projection set, M in {1,2,4,8,16}", "sample": sample},
+            "cpu_baseline": {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
+            "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line))
+
+
+# ----------------------------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------------------------
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="b200")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-prefill", action="store_true", help="skip the prefill extra keys")
+    ap.add_argument("--only", default="", help="debug: run a single part (decode)")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+
+    import torch
+    import torch.distributed as dist
+    from qw38_b200 import _lib as L
+    from qw38_b200 import synth
+    from qw38_b200.q4k_q8 import new_q8_input, pack_q8, q4k_q8_project
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback for the product path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+    L.load()
+    steps, warm = max(1, args.steps), max(3, args.warmup)
+
+    # Row shard of every matrix: multiples of 8 rows (one row group is the unit of the layout).
+    def shard(n):
+        per = (n // 8 + world - 1) // world * 8
+        r0 = min(n, rank * per)
+        return r0, min(n, r0 + per) - r0, per
+
+    layers = []
+    for l in range(LAYERS):
+        mats = []
+        for i, (_, n, k) in enumerate(SHAPES):
+            _, rows, _ = shard(n)
+            mats.append(synth.device_weight(rows, k, seed=1000 * l + 10 * i + rank, device=dev))
+        layers.append(mats)
+
+    g = torch.Generator(device=dev)
+    g.manual_seed(1234)
+    x_in = {m: {k: torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16) for k in (5120, 17408)} for m in TOKENS}
+    q8 = {m: {k: new_q8_input(m, k, dev) for k in (5120, 17408)} for m in TOKENS}
+    failure = torch.zeros(1, dtype=torch.int32, device=dev)
+    outs, gathered = {}, {}
+    for m in TOKENS:
+        for i, (_, n, k) in enumerate(SHAPES):
+            _, rows, per = shard(n)
+            if rows != per:
+                raise SystemExit(f"{n} rows do not split evenly over {world} ranks in row groups of 8")
+            outs[(m, i)] = torch.empty((m, rows), dtype=torch.float32, device=dev)
+            if world > 1:  # rank g's slice lands in gathered[g]; out[t, g*per + j] = gathered[g, t, j]
+                gathered[(m, i)] = torch.empty((world, m, per), dtype=torch.float32, device=dev)
+
+    launches = {"n": 0}
+
+    def projection(m, i, layer, count=True):
+        _, n, k = SHAPES[i]
+        q4k_q8_project(layers[layer][i], q8[m][k], out=outs[(m, i)], trusted=True)
+        if count:
+            launches["n"] += 1
+        if world > 1:
+            dist.all_gather_into_tensor(gathered[(m, i)], outs[(m, i)])
+
+    def one_step(step, count=True, quantise=True, only_kernel=None):
+        for mi, m in enumerate(TOKENS):
+            layer = (step * len(TOKENS) + mi) % LAYERS
+            if quantise:
+                for k in (5120, 17408):
+                    pack_q8(x_in[m][k], failure, out=q8[m][k])
+                    if count:
+                        launches["n"] += 1
+            kern = "dp4a" if m <= 4 else "mma"
+            if only_kernel and kern != only_kernel:
+                continue
+            for i in range(len(SHAPES)):
+                projection(m, i, layer, count)
+
+    stream = torch.cuda.Stream(device=dev)
+
+    def capture(fn, n_steps):
+        """Capture n_steps consecutive steps (distinct layer rotation) into one graph."""
+        with torch.cuda.stream(stream):
+            for s in range(2):
+                fn(s)
+            stream.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for s in range(n_steps):
+                    fn(s)
+        return graph
+
+    def barrier():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    def timed(graph, n_replays):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with torch.cuda.stream(stream):
+            e0.record(stream)
+            for _ in range(n_replays):
+                graph.replay()
+            e1.record(stream)
+        barrier()
+        ms = e0.elapsed_time(e1)
+        if world > 1:
+            t = torch.tensor([ms], dtype=torch.float64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = float(t.item())
+        return ms
+
+    # A graph holds UNROLL steps so that the LAYERS weight copies are all visited.
+    UNROLL = LAYERS
+    use_graph = True
+    try:
+        graph = capture(lambda s: one_step(s, count=False), UNROLL)
+    except Exception as exc:  # NCCL capture can be refused; fall back to eager launches
+        if world == 1:
+            raise
+        use_graph = False
+        print(f"[bench] graph capture unavailable ({type(exc).__name__}); timing eager launches", file=sys.stderr)
+
+    class Eager:
+        def __init__(self, fn, n):
+            self.fn, self.n = fn, n
+
+        def replay(self):
+            for s in range(self.n):
+                self.fn(s)
+
+    if not use_graph:
+        graph = Eager(lambda s: one_step(s, count=False), UNROLL)
+
+    replays = max(1, (steps + UNROLL - 1) // UNROLL)
+    steps = replays * UNROLL  # exactly this many steps are timed
+    warm_replays = max(1, (warm + UNROLL - 1) // UNROLL)
+    timed(graph, warm_replays)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    t0 = time.time()
+    ms = timed(graph, replays)
+    t1 = time.time()
+    clocks = sampler.stop(t0, t1) if rank == 0 else None
+    launches_per_step = len(TOKENS) * (2 + len(SHAPES))
+    total_bytes = step_bytes()
+    value = total_bytes * steps / (ms * 1e-3) / 1e9
+    if failure.item() != 0:
+        raise SystemExit("non-finite activation flagged during the benchmark")
+
+    extra = {}
+    if rank == 0:
+        peaks = {}
+        pk_path = ROOT / "MEASURED_PEAKS.json"
+        if pk_path.exists():
+            peaks = json.loads(pk_path.read_text())
+        hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
+    # Per-kernel passes (all ranks take part so collectives match).
+    per_kernel = {}
+    for kern in ("dp4a", "mma"):
+        ms_list = [m for m in TOKENS if (m <= 4) == (kern == "dp4a")]
+        fn = (lambda s, kk=kern: one_step(s, count=False, quantise=False, only_kernel=kk))
+        gk = capture(fn, UNROLL) if use_graph else Eager(fn, UNROLL)
+        timed(gk, warm_replays)
+        msk = timed(gk, replays)
+        n_launch = len(ms_list) * len(SHAPES) * steps
+        bytes_k = sum(algorithmic_bytes(m, n, k, with_quantise=False) for m in ms_list for _, n, k in SHAPES) * steps
+        per_kernel[kern] = {"launches": n_launch, "avg_us": msk * 1e3 / n_launch, "GBps": bytes_k / (msk * 1e-3) / 1e9,
+                            "ms": msk, "bytes_per_launch": bytes_k / n_launch}
+    per_m = {}
+    if world == 1 and not args.only:
+        for m in TOKENS:
+            def fn(s, mm=m):
+                layer = s % LAYERS
+                for i in range(len(SHAPES)):
+                    projection(mm, i, layer, count=False)
+            gm = capture(fn, UNROLL)
+            timed(gm, 2)
+            mm_ms = timed(gm, max(2, replays // 2))
+            b = sum(algorithmic_bytes(m, n, k, with_quantise=False) for _, n, k in SHAPES) * UNROLL * max(2, replays // 2)
+            per_m[str(m)] = round(b / (mm_ms * 1e-3) / 1e9, 1)
+
+    # End to end: host buffers in, host buffers out, copies inside the timed region.
+    h_in = {m: {k: x_in[m][k].cpu().pin_memory() for k in (5120, 17408)} for m in TOKENS}
+    h_out = {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in (gathered if world > 1 else outs).items()}
+
+    def e2e_step(s):
+        for m in TOKENS:
+            for k in (5120, 17408):
+                x_in[m][k].copy_(h_in[m][k], non_blocking=True)
+        one_step(s, count=False)
+        for key, t in (gathered if world > 1 else outs).items():
+            h_out[key].copy_(t, non_blocking=True)
+
+    ge = capture(e2e_step, UNROLL) if use_graph else Eager(e2e_step, UNROLL)
+    timed(ge, warm_replays)
+    ms_e2e = timed(ge, replays)
+    h2d = sum(m * (5120 + 17408) * 2 for m in TOKENS)
+    d2h = sum(t.numel() * 4 for t in h_out.values())
+    e2e_value = total_bytes * steps / (ms_e2e * 1e-3) / 1e9
+
+    prefill = None
+    if world == 1 and not args.no_prefill and not args.only:
+        prefill = {}
+        for (m, n, k) in [(512, 17408, 5120), (512, 5120, 17408), (2048, 17408, 5120)]:
+            w = synth.device_weight(n, k, seed=99, device=dev)
+            xq = pack_q8(torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16) * 0.5, failure)
+            out = torch.empty((m, n), dtype=torch.float32, device=dev)
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    q4k_q8_project(w, xq, out=out, trusted=True)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                reps = 10
+                e0.record(stream)
+                for _ in range(reps):
+                    q4k_q8_project(w, xq, out=out, trusted=True)
+                e1.record(stream)
+            stream.synchronize()
+            t = e0.elapsed_time(e1) / reps
+            prefill[f"M{m}_N{n}_K{k}"] = {"ms": round(t, 4), "int8_TOPS": round(2.0 * m * n * k / (t * 1e-3) / 1e12, 1)}
+            del w, out, xq
+
+    if rank == 0:
+        dom = max(per_kernel, key=lambda kk: per_kernel[kk]["ms"])
+        pkk = per_kernel[dom]
+        achieved = pkk["GBps"]
+        kernel_name = {"dp4a": "gemv_dp4a_kernel", "mma": "mmq_mma_kernel"}[dom]
+        line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm_replays * UNROLL,
+                "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+                "dtype": "int8 dot / fp32 affine", "data": "synthetic",
+                "config": {"workload": "config[1]: decode projection set QKV 7168x5120, O 5120x5120, gate+up 34816x5120, "
+                                       "down 5120x17408, Q4_K weights, M in {1,2,4,8,16}, bf16 activations quantised on device",
+                           "layers_rotated": LAYERS, "l2": f"weights rotate over {LAYERS} layer copies (1.49 GB) > 126 MB L2",
+                           "parallelism": f"rows/{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                           "launch": "CUDA graph replay" if use_graph else "eager",
+                           "bytes_per_step": total_bytes},
+                "clocks": clocks, "gpu_launches": launches_per_step * steps,
+                "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                        "ms_per_step": ms_e2e / steps},
+                "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
+                             "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
+                             "avg_launch_us": pkk["avg_us"], "bytes_per_launch": pkk["bytes_per_launch"],
+                             "by_kernel": {kk: {"GBps": round(v["GBps"], 1), "frac": round(v["GBps"] / hbm_peak, 4),
+                                                "avg_us": round(v["avg_us"], 3), "launches": v["launches"]}
+                                           for kk, v in per_kernel.items()}},
+                "decode_GBps_by_tokens": per_m, "prefill": prefill}
+        if not args.no_cpu and world == 1:
+            gbps, cores, sample = cpu_sample(3)
+            line["cpu_baseline"] = {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}
+        else:
+            line["cpu_baseline"] = None
+        print(json.dumps(line))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

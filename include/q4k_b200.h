@@ -1,0 +1,174 @@
+/*
+ * q4k_b200 -- C ABI of the B200 (sm_100a) Q4_K weight x Q8 activation matmul engine.
+ *
+ * Every entry point takes plain pointers and sizes, enqueues work on the given
+ * CUDA stream (a cudaStream_t passed as void*) and returns a status code.  All
+ * device pointers are borrowed and must stay alive until the enqueued work has
+ * completed.  Unless stated otherwise nothing is allocated and nothing
+ * synchronises, so the calls can be recorded into a CUDA graph.
+ *
+ * Each declaration names the interface of the reference engine (Enucatl/qw38)
+ * that it stands behind, as file:line inside that project.
+ */
+#ifndef Q4K_B200_H_
+#define Q4K_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Status codes; 1..3 are the reference's ErrorCode values (cuda/error.hpp:13-17). */
+#define Q4K_OK 0
+#define Q4K_ERR_STATUS 1           /* a CUDA call failed; see q4k_last_cuda_status() */
+#define Q4K_ERR_INVALID_ARGUMENT 2 /* rejected before any device work */
+#define Q4K_ERR_OVERFLOW 3         /* address or size arithmetic overflow */
+
+/* Wire ids of the one supported weight format (cuda/decode_mmv.hpp:31,41). */
+#define Q4K_LAYOUT_SPLIT_TILES 0x020D
+#define Q4K_QUANTIZER_Q4K 0x0105
+
+/* Limits.  The reference stops at m<=512, n,k<=17408 (cuda/q4k_q8.cu:286-298);
+ * this library lifts them to the benchmark configurations. */
+#define Q4K_MAX_TOKENS 16384u
+#define Q4K_MAX_N 262144u
+#define Q4K_MAX_K 32768u
+#define Q4K_DOT_BOUND (32 * 15 * 127) /* cuda/q4k_q8.hpp:23 */
+#define Q4K_SUM_BOUND (32 * 127)      /* cuda/q4k_q8.hpp:24 */
+
+/* Q4_K weight matrix in the reference's split-tile device layout
+ * (struct PrefillWeight, cuda/prefill.hpp:33-44; layout src/format/pack.cpp:175-222):
+ *   codes : padded_n*padded_k/2 bytes, tile row ((row/8)*(padded_k/256)+kb)*8+row%8
+ *           holds 128 bytes, byte j = columns 256kb+2j (low nibble), 256kb+2j+1 (high);
+ *   scales: 16 bytes per tile row = fp16 d, fp16 dmin, 12 packed 6-bit scale/min bytes.
+ * padded_n = ceil8(n), padded_k = ceil256(k); padding holds zero codes and metadata. */
+typedef struct q4k_weight {
+  const void* codes;
+  const void* scales;
+  uint16_t layout;    /* Q4K_LAYOUT_SPLIT_TILES */
+  uint16_t quantizer; /* Q4K_QUANTIZER_Q4K */
+  uint32_t n, k, padded_n, padded_k;
+  uint64_t codes_bytes, scales_bytes;
+} q4k_weight;
+
+/* Quantised activations (struct Q8Input, cuda/q4k_q8.hpp:14-21): row-major
+ * codes[m][padded_k], fp32 scales[m][padded_k/32], exact int32 sums[m][padded_k/32].
+ * The *_len fields are element counts, as the spans' size() in the reference. */
+typedef struct q4k_q8_input {
+  int8_t* codes;
+  float* scales;
+  int32_t* sums;
+  uint64_t codes_len, scales_len, sums_len;
+  uint32_t m, k, padded_k;
+} q4k_q8_input;
+
+/* Which kernel family q4k_q8_project_ex runs; 0 lets the library choose by m
+ * (the reference's switch m==1 | m>=128 | else is cuda/q4k_q8.cu:303-313). */
+#define Q4K_KERNEL_AUTO 0
+#define Q4K_KERNEL_GEMV_DP4A 1 /* m <= 4 : dp4a, one lane per K32 group */
+#define Q4K_KERNEL_MMA 2       /* any m  : warp-level int8 mma, per-K32 reset */
+#define Q4K_KERNEL_TCGEN05 3   /* m >= 32: tcgen05 kind::i8, TMEM accumulators */
+
+typedef struct q4k_project_options {
+  uint32_t kernel;       /* Q4K_KERNEL_* */
+  uint32_t split_k;      /* 0 = choose; otherwise number of K slices (mma kernel) */
+  int32_t* partials;     /* optional: int32 dots [m][n][padded_k/32], bit-exact check */
+  uint64_t partials_len; /* element count of partials, m*n*padded_k/32 when given */
+  void* workspace;       /* optional scratch for split-K; NULL = library-owned scratch */
+  uint64_t workspace_bytes;
+  uint32_t flags;        /* Q4K_FLAG_* */
+} q4k_project_options;
+
+/* Skip the per-call device-span checks (pointer attributes, allocation bounds); geometry
+ * and overlap checks still run.  For callers that validated the same buffers once. */
+#define Q4K_FLAG_TRUSTED_SPANS 1u
+
+const char* q4k_last_error(void);   /* thread-local text of the last failure */
+int q4k_last_cuda_status(void);     /* cudaError_t of the last Q4K_ERR_STATUS */
+uint32_t q4k_abi_version(void);
+
+/* Padding rules (decode_pad_n / decode_pad_k / decode_code_bytes / decode_scale_bytes,
+ * cuda/decode_mmv.hpp:148-205, Q4_K branch). */
+uint64_t q4k_pad_n(uint32_t n);
+uint32_t q4k_pad_k(uint32_t k);
+uint64_t q4k_code_bytes(uint32_t padded_n, uint32_t padded_k);
+uint64_t q4k_scale_bytes(uint32_t padded_n, uint32_t padded_k);
+
+/* validate_prefill_device_span (cuda/prefill.hpp:28-31, cuda/prefill.cu:329-335):
+ * device pointer on `device`, aligned, inside one allocation. */
+int q4k_validate_device_span(const void* pointer, uint64_t bytes, uint32_t alignment, int device);
+
+/* pack_q8 (cuda/q4k_q8.hpp:32-34, cuda/q4k_q8.cu:318-330): bf16 [m][k] -> Q8.
+ * `failure` is one int in device memory, set to 1 by any K32 group that holds a
+ * non-finite value; the owner clears it before and reads it after. */
+int q4k_pack_q8_bf16(const uint16_t* input, uint64_t input_len, q4k_q8_input output,
+                     int* failure, void* stream);
+/* Same producer for fp32 rows (the single-GEMV benchmark configuration feeds fp32;
+ * the device routine is the reference's q8_pack_warp, cuda/q8_device.cuh:5-25). */
+int q4k_pack_q8_f32(const float* input, uint64_t input_len, q4k_q8_input output,
+                    int* failure, void* stream);
+
+/* 36-byte "Q8_1" records {fp16 d, fp16 s, int8 q[32]} from an exact pack:
+ * d = fp16_rn(scale), s = fp16_rn(scale * sum).  No counterpart in the reference,
+ * whose activations stay in the exact fp32/int32 form (cuda/q4k_q8.hpp:14-21). */
+int q4k_export_q8_1(q4k_q8_input input, uint8_t* records, uint64_t records_bytes, void* stream);
+
+/* q4k_q8_project (cuda/q4k_q8.hpp:35-37, cuda/q4k_q8.cu:332-345):
+ * out[token*n + row] = sum_g a[token,g]*((d*sc_g)*dot_g - (dmin*m_g)*sum[token,g]) (+ residual).
+ * residual may be NULL (residual_len 0).  The first call on a device may allocate the
+ * library-owned split-K scratch; make one call per device before capturing a graph. */
+int q4k_q8_project(const q4k_weight* weight, q4k_q8_input input, float* output,
+                   uint64_t output_len, const float* residual, uint64_t residual_len,
+                   void* stream);
+int q4k_q8_project_ex(const q4k_weight* weight, q4k_q8_input input, float* output,
+                      uint64_t output_len, const float* residual, uint64_t residual_len,
+                      const q4k_project_options* options, void* stream);
+/* Scratch bytes q4k_q8_project_ex needs for (m, n, split_k); 0 when split_k <= 1. */
+uint64_t q4k_project_workspace_bytes(uint32_t m, uint32_t n, uint32_t split_k);
+
+/* Ragged continuous batch: requests r = 0..n_requests-1 own the packed token rows
+ * [row_offsets[r], row_offsets[r+1]) of one Q8 pack with m = row_offsets[n_requests].
+ * The projection is row independent and position free (cuda/prefill.hpp:58-60), so
+ * this is q4k_q8_project over the packed rows; row_offsets (host memory) is validated
+ * (monotone, covering m) and each request's rows equal the same rows run alone.
+ * The reference is single-sequence and has no such entry (its closest statement is
+ * the token<m masking of cuda/q4k_q8.cu:137-141). */
+int q4k_q8_project_ragged(const q4k_weight* weight, q4k_q8_input input,
+                          const uint32_t* row_offsets, uint32_t n_requests, float* output,
+                          uint64_t output_len, const q4k_project_options* options, void* stream);
+
+/* 144-byte llama.cpp-native super-blocks [n][k/256] (k % 256 == 0, device memory)
+ * -> split tiles, padded rows zeroed.  Resident prepare-once step; the reference
+ * does the same permutation on the host (src/format/pack.cpp:175-222 fed by
+ * third_party/llama.cpp-q4k/reference.hpp:244-248 element order). */
+int q4k_repack_blocks144(const uint8_t* blocks, uint64_t blocks_bytes, uint32_t n, uint32_t k,
+                         uint8_t* out_codes, uint64_t out_codes_bytes, uint8_t* out_scales,
+                         uint64_t out_scales_bytes, void* stream);
+
+/* q8_mlp_workspace_bytes (cuda/q4k_q8.hpp:28-30), generalised from 17408/5120 to (ffn, hidden). */
+uint64_t q4k_q8_mlp_workspace_bytes(uint32_t m, uint32_t hidden, uint32_t ffn);
+
+/* q4k_q8_mlp (cuda/q4k_q8.hpp:44-49, cuda/q4k_q8.cu:347-398): RMS norm + Q8 pack ->
+ * gate -> up -> SwiGLU + Q8 pack -> down + residual, one sticky failure flag.
+ * With pending_failure == NULL the call clears, reads back and checks the flag
+ * (synchronising the stream) and returns Q4K_ERR_INVALID_ARGUMENT for a non-finite
+ * producer; otherwise it only enqueues.  *submitted is 0 for a pre-launch rejection
+ * and 1 once device work was attempted. */
+int q4k_q8_mlp(const q4k_weight* gate, const q4k_weight* up, const q4k_weight* down,
+               const float* residual, const uint16_t* gamma, float eps, float* output,
+               uint32_t m, void* workspace, uint64_t workspace_bytes, void* stream,
+               int* submitted, int* pending_failure);
+
+/* launch_hidden_rms_q8 (cuda/activation.cu:536-548, kernel :134-190). */
+int q4k_hidden_rms_q8(const float* residual, const uint16_t* gamma, float eps, uint32_t m,
+                      uint32_t hidden, q4k_q8_input output, int* failure, void* stream);
+/* swiglu_pack_kernel (cuda/q4k_q8.cu:52-61). */
+int q4k_swiglu_pack_q8(const float* gate, const float* up, uint32_t m, uint32_t ffn,
+                       q4k_q8_input output, int* failure, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4K_B200_H_ */

@@ -1,0 +1,421 @@
+// C-ABI layer: argument validation, regime dispatch and scratch ownership.
+//
+// Validation follows the reference's host checks: geometry (valid_input / valid_weight,
+// cuda/q4k_q8.cu:286-298), device-span membership (device_region, cuda/prefill.cu:273-309)
+// and pairwise non-overlap of live operands (distinct, cuda/q4k_q8.cu:270-285).  A call
+// rejected here has launched nothing and left every device buffer untouched.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cmath>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <limits>
+#include <mutex>
+
+#include "../../include/q4k_b200.h"
+#include "launch.h"
+
+namespace {
+
+thread_local char g_error[512] = "";
+thread_local int g_cuda_status = 0;
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+  return code;
+}
+int fail_cuda(cudaError_t st, const char* op) {
+  (void)cudaGetLastError();  // consume the sticky status, as the reference's check() does
+  g_cuda_status = int(st);
+  return fail(Q4K_ERR_STATUS, "%s: %s", op, cudaGetErrorString(st));
+}
+#define Q4K_CUDA(expr, op)                                  \
+  do {                                                      \
+    cudaError_t st__ = (expr);                              \
+    if (st__ != cudaSuccess) return fail_cuda(st__, op);    \
+  } while (0)
+
+using MemGetAddressRange = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
+MemGetAddressRange address_range_fn() {
+  static MemGetAddressRange fn = [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuMemGetAddressRange", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      p = nullptr;
+    (void)cudaGetLastError();
+    return reinterpret_cast<MemGetAddressRange>(p);
+  }();
+  return fn;
+}
+
+struct Region {
+  const void* p;
+  uint64_t bytes;
+  uint32_t alignment;
+  const char* name;
+};
+
+int check_span(const Region& r, int device) {
+  auto const begin = reinterpret_cast<uintptr_t>(r.p);
+  if (!r.p || r.bytes == 0) return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: empty span", r.name);
+  if (r.bytes > std::numeric_limits<uintptr_t>::max() - begin)
+    return fail(Q4K_ERR_OVERFLOW, "%s: address overflow", r.name);
+  if (r.alignment == 0 || begin % r.alignment != 0)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: misaligned pointer", r.name);
+  cudaPointerAttributes attr{};
+  if (cudaPointerGetAttributes(&attr, r.p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: pointer is not device memory", r.name);
+  }
+  if (attr.type != cudaMemoryTypeDevice || attr.device != device)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: not device memory of the current device", r.name);
+  if (auto fn = address_range_fn()) {
+    CUdeviceptr base = 0;
+    size_t size = 0;
+    if (fn(&base, &size, static_cast<CUdeviceptr>(begin)) != CUDA_SUCCESS)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: unknown device allocation", r.name);
+    if (begin < base || begin + r.bytes > base + size)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: operand exceeds its allocation", r.name);
+  }
+  return Q4K_OK;
+}
+
+int check_distinct(const Region* regions, int count, bool trusted) {
+  int device = 0;
+  if (!trusted) Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+  for (int i = 0; i < count; ++i) {
+    if (!trusted) {
+      if (int st = check_span(regions[i], device)) return st;
+    } else if (!regions[i].p) {
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: null pointer", regions[i].name);
+    }
+    auto const b = reinterpret_cast<uintptr_t>(regions[i].p);
+    for (int j = 0; j < i; ++j) {
+      auto const c = reinterpret_cast<uintptr_t>(regions[j].p);
+      if (b < c + regions[j].bytes && c < b + regions[i].bytes)
+        return fail(Q4K_ERR_INVALID_ARGUMENT, "live operands overlap: %s and %s", regions[i].name, regions[j].name);
+    }
+  }
+  return Q4K_OK;
+}
+
+bool valid_input(const q4k_q8_input& x) {
+  return x.m && x.m <= Q4K_MAX_TOKENS && x.k && x.k <= Q4K_MAX_K && x.padded_k == q4k_pad_k(x.k) &&
+         x.codes_len == uint64_t(x.m) * x.padded_k && x.scales_len == x.codes_len / 32 &&
+         x.sums_len == x.scales_len;
+}
+
+int valid_weight(const q4k_weight* w, const char* name) {
+  if (!w) return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: null weight", name);
+  if (!w->n || w->n > Q4K_MAX_N || !w->k || w->k > Q4K_MAX_K || w->layout != Q4K_LAYOUT_SPLIT_TILES ||
+      w->quantizer != Q4K_QUANTIZER_Q4K || w->padded_n != q4k_pad_n(w->n) || w->padded_k != q4k_pad_k(w->k) ||
+      w->codes_bytes != q4k_code_bytes(w->padded_n, w->padded_k) ||
+      w->scales_bytes != q4k_scale_bytes(w->padded_n, w->padded_k))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "%s: Q4_K split-tile geometry required", name);
+  return Q4K_OK;
+}
+
+q4k::WeightView view(const q4k_weight& w) {
+  return {static_cast<const uint8_t*>(w.codes), static_cast<const uint8_t*>(w.scales), w.n, w.padded_n,
+          w.padded_k / 256};
+}
+q4k::Q8View view(const q4k_q8_input& x) { return {x.codes, x.scales, x.sums, x.m, x.padded_k}; }
+q4k::Q8Out out_view(const q4k_q8_input& x) { return {x.codes, x.scales, x.sums, x.m, x.padded_k}; }
+
+// Library-owned split-K scratch, one per device: [ticket region | fp32 partial tiles].
+// Tickets are zeroed at allocation and every kernel leaves them zero.
+constexpr uint64_t kTicketRegion = 256 * 1024;
+struct Scratch {
+  void* p = nullptr;
+  uint64_t bytes = 0;
+};
+std::mutex g_scratch_mutex;
+Scratch g_scratch[64];
+
+int own_scratch(uint64_t partial_bytes, void** out) {
+  int device = 0;
+  Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+  if (device < 0 || device >= 64) return fail(Q4K_ERR_INVALID_ARGUMENT, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  Scratch& s = g_scratch[device];
+  uint64_t const need = kTicketRegion + partial_bytes;
+  if (s.bytes < need) {
+    // Growing synchronises the device: earlier launches may still use the old block.
+    Q4K_CUDA(cudaDeviceSynchronize(), "scratch.sync");
+    if (s.p) Q4K_CUDA(cudaFree(s.p), "scratch.free");
+    s = Scratch{};
+    uint64_t const bytes = need < (8ull << 20) ? (8ull << 20) : (need + (1ull << 20) - 1) / (1ull << 20) * (1ull << 20);
+    Q4K_CUDA(cudaMalloc(&s.p, bytes), "scratch.alloc");
+    Q4K_CUDA(cudaMemset(s.p, 0, kTicketRegion), "scratch.clear");
+    s.bytes = bytes;
+  }
+  *out = s.p;
+  return Q4K_OK;
+}
+
+constexpr uint32_t kFlagTrustedSpans = 1u;
+
+int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output, uint64_t output_len,
+                 const float* residual, uint64_t residual_len, const q4k_project_options* opt,
+                 cudaStream_t stream) {
+  if (int st = valid_weight(weight, "weight")) return st;
+  const q4k_weight& w = *weight;
+  if (!valid_input(x) || x.k != w.k || output_len != uint64_t(x.m) * w.n ||
+      (residual_len != 0 && residual_len != output_len) || (residual_len != 0 && !residual))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: invalid geometry");
+  uint32_t const G = x.padded_k / 32;
+  int32_t* partials = opt ? opt->partials : nullptr;
+  if (partials && opt->partials_len != uint64_t(x.m) * w.n * G)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: partials length must be m*n*padded_k/32");
+  bool const trusted = opt && (opt->flags & kFlagTrustedSpans);
+  Region regions[8] = {{w.codes, w.codes_bytes, 4, "weight.codes"},
+                       {w.scales, w.scales_bytes, 2, "weight.scales"},
+                       {x.codes, x.codes_len, 4, "input.codes"},
+                       {x.scales, x.scales_len * 4, 4, "input.scales"},
+                       {x.sums, x.sums_len * 4, 4, "input.sums"},
+                       {output, output_len * 4, 4, "output"},
+                       {nullptr, 0, 4, ""},
+                       {nullptr, 0, 4, ""}};
+  int count = 6;
+  if (residual_len) regions[count++] = {residual, residual_len * 4, 4, "residual"};
+  if (partials) regions[count++] = {partials, opt->partials_len * 4, 4, "partials"};
+  if (int st = check_distinct(regions, count, trusted)) return st;
+
+  uint32_t kernel = opt ? opt->kernel : Q4K_KERNEL_AUTO;
+  if (kernel == Q4K_KERNEL_AUTO) kernel = x.m <= q4k::kGemvDp4aMaxTokens ? Q4K_KERNEL_GEMV_DP4A : Q4K_KERNEL_MMA;
+  const float* res = residual_len ? residual : nullptr;
+  if (kernel == Q4K_KERNEL_GEMV_DP4A) {
+    if (x.m > q4k::kGemvDp4aMaxTokens) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: dp4a kernel takes m <= 4");
+    Q4K_CUDA(q4k::launch_gemv_dp4a(view(w), view(x), output, res, partials, stream), "q4k_q8.gemv_dp4a");
+    return Q4K_OK;
+  }
+  if (kernel == Q4K_KERNEL_MMA) {
+    q4k::MmaPlan plan = q4k::plan_mma(x.m, w.n, w.padded_k / 256, opt ? opt->split_k : 0);
+    void* scratch = nullptr;
+    if (plan.split_k > 1) {
+      uint64_t const row_tiles = (w.padded_n / 8 + 7) / 8, token_tiles = (x.m + plan.token_tile - 1) / plan.token_tile;
+      if (row_tiles * token_tiles * 4 > kTicketRegion)
+        return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: too many tiles for split-K");
+      uint64_t const partial_bytes = uint64_t(plan.split_k) * x.m * w.n * 4;
+      if (opt && opt->workspace) {
+        if (opt->workspace_bytes < kTicketRegion + partial_bytes)
+          return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: workspace too small");
+        if (!trusted) {
+          Region ws{opt->workspace, opt->workspace_bytes, 256, "workspace"};
+          int device = 0;
+          Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+          if (int st = check_span(ws, device)) return st;
+        }
+        scratch = opt->workspace;
+        Q4K_CUDA(cudaMemsetAsync(scratch, 0, row_tiles * token_tiles * 4, stream), "q4k_q8.clear_tickets");
+      } else if (int st = own_scratch(partial_bytes, &scratch)) {
+        return st;
+      }
+    }
+    Q4K_CUDA(q4k::launch_mmq_mma(view(w), view(x), output, res, partials, plan,
+                                 scratch ? static_cast<uint8_t*>(scratch) + kTicketRegion : nullptr,
+                                 static_cast<uint32_t*>(scratch), stream),
+             "q4k_q8.mmq_mma");
+    return Q4K_OK;
+  }
+  return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: unknown kernel selector %u", kernel);
+}
+
+int pack_impl(const void* input, bool fp32, uint64_t input_len, const q4k_q8_input& x, int* failure,
+              cudaStream_t stream) {
+  if (!valid_input(x) || input_len != uint64_t(x.m) * x.k || !failure)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.pack: invalid geometry");
+  Region regions[5] = {{input, input_len * (fp32 ? 4u : 2u), fp32 ? 4u : 2u, "input"},
+                       {x.codes, x.codes_len, 4, "output.codes"},
+                       {x.scales, x.scales_len * 4, 4, "output.scales"},
+                       {x.sums, x.sums_len * 4, 4, "output.sums"},
+                       {failure, 4, 4, "failure"}};
+  if (int st = check_distinct(regions, 5, false)) return st;
+  Q4K_CUDA(q4k::launch_pack_q8(input, fp32, out_view(x), x.k, failure, stream), "q8.pack");
+  return Q4K_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* q4k_last_error(void) { return g_error; }
+int q4k_last_cuda_status(void) { return g_cuda_status; }
+uint32_t q4k_abi_version(void) { return 1; }
+
+uint64_t q4k_pad_n(uint32_t n) { return n == 0 ? 0 : (uint64_t(n) + 7) / 8 * 8; }
+uint32_t q4k_pad_k(uint32_t k) { return k == 0 ? 0 : (k + 255u) / 256u * 256u; }
+uint64_t q4k_code_bytes(uint32_t padded_n, uint32_t padded_k) { return uint64_t(padded_n) * padded_k / 2; }
+uint64_t q4k_scale_bytes(uint32_t padded_n, uint32_t padded_k) { return uint64_t(padded_n) * (padded_k / 256) * 16; }
+
+int q4k_validate_device_span(const void* pointer, uint64_t bytes, uint32_t alignment, int device) {
+  return check_span(Region{pointer, bytes, alignment, "span"}, device);
+}
+
+int q4k_pack_q8_bf16(const uint16_t* input, uint64_t input_len, q4k_q8_input output, int* failure, void* stream) {
+  return pack_impl(input, false, input_len, output, failure, static_cast<cudaStream_t>(stream));
+}
+int q4k_pack_q8_f32(const float* input, uint64_t input_len, q4k_q8_input output, int* failure, void* stream) {
+  return pack_impl(input, true, input_len, output, failure, static_cast<cudaStream_t>(stream));
+}
+
+int q4k_export_q8_1(q4k_q8_input x, uint8_t* records, uint64_t records_bytes, void* stream) {
+  if (!valid_input(x) || records_bytes != x.scales_len * 36)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.export: invalid geometry");
+  Region regions[4] = {{x.codes, x.codes_len, 4, "input.codes"},
+                       {x.scales, x.scales_len * 4, 4, "input.scales"},
+                       {x.sums, x.sums_len * 4, 4, "input.sums"},
+                       {records, records_bytes, 4, "records"}};
+  if (int st = check_distinct(regions, 4, false)) return st;
+  Q4K_CUDA(q4k::launch_export_q8_1(x.codes, x.scales, x.sums, x.scales_len, records, static_cast<cudaStream_t>(stream)),
+           "q8.export");
+  return Q4K_OK;
+}
+
+int q4k_q8_project(const q4k_weight* weight, q4k_q8_input input, float* output, uint64_t output_len,
+                   const float* residual, uint64_t residual_len, void* stream) {
+  return project_impl(weight, input, output, output_len, residual, residual_len, nullptr,
+                      static_cast<cudaStream_t>(stream));
+}
+int q4k_q8_project_ex(const q4k_weight* weight, q4k_q8_input input, float* output, uint64_t output_len,
+                      const float* residual, uint64_t residual_len, const q4k_project_options* options,
+                      void* stream) {
+  return project_impl(weight, input, output, output_len, residual, residual_len, options,
+                      static_cast<cudaStream_t>(stream));
+}
+
+uint64_t q4k_project_workspace_bytes(uint32_t m, uint32_t n, uint32_t split_k) {
+  return split_k <= 1 ? 0 : kTicketRegion + uint64_t(split_k) * m * n * 4;
+}
+
+int q4k_q8_project_ragged(const q4k_weight* weight, q4k_q8_input input, const uint32_t* row_offsets,
+                          uint32_t n_requests, float* output, uint64_t output_len,
+                          const q4k_project_options* options, void* stream) {
+  if (!row_offsets || n_requests == 0) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.ragged: no requests");
+  if (row_offsets[0] != 0) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.ragged: row_offsets[0] must be 0");
+  for (uint32_t r = 0; r < n_requests; ++r)
+    if (row_offsets[r + 1] <= row_offsets[r])
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.ragged: request %u is empty or offsets decrease", r);
+  if (row_offsets[n_requests] != input.m)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.ragged: offsets cover %u rows, pack holds %u", row_offsets[n_requests], input.m);
+  return project_impl(weight, input, output, output_len, nullptr, 0, options, static_cast<cudaStream_t>(stream));
+}
+
+int q4k_repack_blocks144(const uint8_t* blocks, uint64_t blocks_bytes, uint32_t n, uint32_t k, uint8_t* out_codes,
+                         uint64_t out_codes_bytes, uint8_t* out_scales, uint64_t out_scales_bytes, void* stream) {
+  if (!n || n > Q4K_MAX_N || !k || k > Q4K_MAX_K || k % 256 != 0 || blocks_bytes != uint64_t(n) * (k / 256) * 144 ||
+      out_codes_bytes != q4k_code_bytes(uint32_t(q4k_pad_n(n)), k) ||
+      out_scales_bytes != q4k_scale_bytes(uint32_t(q4k_pad_n(n)), k))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q4k.repack: invalid geometry");
+  Region regions[3] = {{blocks, blocks_bytes, 1, "blocks"},
+                       {out_codes, out_codes_bytes, 16, "codes"},
+                       {out_scales, out_scales_bytes, 16, "scales"}};
+  if (int st = check_distinct(regions, 3, false)) return st;
+  Q4K_CUDA(q4k::launch_repack_blocks144(blocks, n, k, out_codes, out_scales, static_cast<cudaStream_t>(stream)),
+           "q4k.repack");
+  return Q4K_OK;
+}
+
+uint64_t q4k_q8_mlp_workspace_bytes(uint32_t m, uint32_t hidden, uint32_t ffn) {
+  (void)hidden;  // the hidden-width pack reuses the front of the ffn-width pack
+  return uint64_t(m) * (uint64_t(ffn) + uint64_t(ffn) / 32 * 8 + 2ull * ffn * 4) + 4;
+}
+
+int q4k_hidden_rms_q8(const float* residual, const uint16_t* gamma, float eps, uint32_t m, uint32_t hidden,
+                      q4k_q8_input x, int* failure, void* stream) {
+  if (!residual || !gamma || !failure || !m || !hidden || hidden % 256 != 0 || hidden > Q4K_MAX_K ||
+      !std::isfinite(eps) || eps <= 0 || !valid_input(x) || x.m != m || x.k != hidden)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.rms: invalid operands");
+  Region regions[6] = {{residual, uint64_t(m) * hidden * 4, 4, "residual"}, {gamma, uint64_t(hidden) * 2, 2, "gamma"},
+                       {x.codes, x.codes_len, 4, "output.codes"},          {x.scales, x.scales_len * 4, 4, "output.scales"},
+                       {x.sums, x.sums_len * 4, 4, "output.sums"},         {failure, 4, 4, "failure"}};
+  if (int st = check_distinct(regions, 6, false)) return st;
+  Q4K_CUDA(q4k::launch_hidden_rms_q8(residual, gamma, eps, hidden, out_view(x), failure, static_cast<cudaStream_t>(stream)),
+           "q8.rms_pack");
+  return Q4K_OK;
+}
+
+int q4k_swiglu_pack_q8(const float* gate, const float* up, uint32_t m, uint32_t ffn, q4k_q8_input x, int* failure,
+                       void* stream) {
+  if (!gate || !up || !failure || !m || !ffn || ffn % 256 != 0 || !valid_input(x) || x.m != m || x.k != ffn)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.swiglu_pack: invalid operands");
+  Region regions[6] = {{gate, uint64_t(m) * ffn * 4, 16, "gate"},  {up, uint64_t(m) * ffn * 4, 16, "up"},
+                       {x.codes, x.codes_len, 4, "output.codes"}, {x.scales, x.scales_len * 4, 4, "output.scales"},
+                       {x.sums, x.sums_len * 4, 4, "output.sums"}, {failure, 4, 4, "failure"}};
+  if (int st = check_distinct(regions, 6, false)) return st;
+  Q4K_CUDA(q4k::launch_swiglu_pack_q8(gate, up, out_view(x), failure, static_cast<cudaStream_t>(stream)), "q8.swiglu_pack");
+  return Q4K_OK;
+}
+
+int q4k_q8_mlp(const q4k_weight* gate, const q4k_weight* up, const q4k_weight* down, const float* residual,
+               const uint16_t* gamma, float eps, float* output, uint32_t m, void* workspace, uint64_t workspace_bytes,
+               void* stream_v, int* submitted, int* pending_failure) {
+  auto stream = static_cast<cudaStream_t>(stream_v);
+  if (!submitted) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.mlp: submitted must not be null");
+  *submitted = 0;
+  if (!pending_failure) {
+    // The synchronous form reads the flag back, which a capturing stream cannot do.
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    Q4K_CUDA(cudaStreamIsCapturing(stream, &cap), "q8.mlp.capture_status");
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.mlp: synchronous form needs an uncaptured stream");
+  }
+  for (auto const* w : {gate, up, down})
+    if (int st = valid_weight(w, "mlp weight")) return st;
+  uint32_t const hidden = gate->k, ffn = gate->n;
+  if (!m || m > Q4K_MAX_TOKENS || !workspace || workspace_bytes < q4k_q8_mlp_workspace_bytes(m, hidden, ffn) ||
+      !std::isfinite(eps) || eps <= 0 || hidden % 256 != 0 || ffn % 256 != 0 || up->n != ffn || up->k != hidden ||
+      down->n != hidden || down->k != ffn)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.mlp: invalid geometry");
+  Region regions[11] = {{gate->codes, gate->codes_bytes, 4, "gate.codes"},   {gate->scales, gate->scales_bytes, 2, "gate.scales"},
+                        {up->codes, up->codes_bytes, 4, "up.codes"},         {up->scales, up->scales_bytes, 2, "up.scales"},
+                        {down->codes, down->codes_bytes, 4, "down.codes"},   {down->scales, down->scales_bytes, 2, "down.scales"},
+                        {residual, uint64_t(m) * hidden * 4, 4, "residual"}, {gamma, uint64_t(hidden) * 2, 2, "gamma"},
+                        {output, uint64_t(m) * hidden * 4, 4, "output"},     {workspace, workspace_bytes, 16, "workspace"},
+                        {pending_failure, 4, 4, "pending_failure"}};
+  if (int st = check_distinct(regions, pending_failure ? 11 : 10, false)) return st;
+
+  // Workspace carve-up, in the reference's order (cuda/q4k_q8.cu:367-372).
+  auto* codes = static_cast<int8_t*>(workspace);
+  auto* scales = reinterpret_cast<float*>(codes + uint64_t(m) * ffn);
+  auto* sums = reinterpret_cast<int32_t*>(scales + uint64_t(m) * (ffn / 32));
+  auto* g = reinterpret_cast<float*>(sums + uint64_t(m) * (ffn / 32));
+  auto* u = g + uint64_t(m) * ffn;
+  int* failure = pending_failure ? pending_failure : reinterpret_cast<int*>(u + uint64_t(m) * ffn);
+  *submitted = 1;
+  auto bail = [&](int st) {
+    if (!pending_failure) (void)cudaStreamSynchronize(stream);
+    return st;
+  };
+  if (!pending_failure) {
+    cudaError_t st = cudaMemsetAsync(failure, 0, 4, stream);
+    if (st != cudaSuccess) return bail(fail_cuda(st, "q8.clear_failure"));
+  }
+  q4k_q8_input xh{codes, scales, sums, uint64_t(m) * hidden, uint64_t(m) * (hidden / 32), uint64_t(m) * (hidden / 32), m, hidden, hidden};
+  q4k_q8_input xf{codes, scales, sums, uint64_t(m) * ffn, uint64_t(m) * (ffn / 32), uint64_t(m) * (ffn / 32), m, ffn, ffn};
+  q4k_project_options opt{};
+  opt.flags = kFlagTrustedSpans;  // every span was validated above
+  cudaError_t ce = q4k::launch_hidden_rms_q8(residual, gamma, eps, hidden, out_view(xh), failure, stream);
+  if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.rms_pack"));
+  if (int st = project_impl(gate, xh, g, uint64_t(m) * ffn, nullptr, 0, &opt, stream)) return bail(st);
+  if (int st = project_impl(up, xh, u, uint64_t(m) * ffn, nullptr, 0, &opt, stream)) return bail(st);
+  ce = q4k::launch_swiglu_pack_q8(g, u, out_view(xf), failure, stream);
+  if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.swiglu_pack"));
+  if (int st = project_impl(down, xf, output, uint64_t(m) * hidden, residual, uint64_t(m) * hidden, &opt, stream))
+    return bail(st);
+  if (pending_failure) return Q4K_OK;
+  int bad = 0;
+  ce = cudaMemcpyAsync(&bad, failure, 4, cudaMemcpyDeviceToHost, stream);
+  if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.failure"));
+  Q4K_CUDA(cudaStreamSynchronize(stream), "q8.mlp.sync");
+  if (bad) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.producer: nonfinite producer or invalid Q8 scale");
+  return Q4K_OK;
+}
+
+}  // extern "C"

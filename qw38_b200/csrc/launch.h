@@ -1,0 +1,50 @@
+// Internal launch interface between the C-ABI layer (abi.cu) and the kernel files.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "common.cuh"
+
+namespace q4k {
+
+struct Q8Out {
+  int8_t* codes;
+  float* scales;
+  int32_t* sums;
+  uint32_t m, padded_k;
+};
+
+// q8_quantize.cu
+cudaError_t launch_pack_q8(const void* input, bool fp32, Q8Out out, uint32_t k, int* failure,
+                           cudaStream_t stream);
+cudaError_t launch_swiglu_pack_q8(const float* gate, const float* up, Q8Out out, int* failure,
+                                  cudaStream_t stream);
+cudaError_t launch_hidden_rms_q8(const float* residual, const uint16_t* gamma, float eps,
+                                 uint32_t hidden, Q8Out out, int* failure, cudaStream_t stream);
+cudaError_t launch_export_q8_1(const int8_t* codes, const float* scales, const int32_t* sums,
+                               uint64_t groups, uint8_t* records, cudaStream_t stream);
+
+// gemv_dp4a.cu : m <= 4.  partials (optional) receives the int32 K32 dots [m][n][G].
+cudaError_t launch_gemv_dp4a(const WeightView& w, const Q8View& x, float* out,
+                             const float* residual, int32_t* partials, cudaStream_t stream);
+constexpr uint32_t kGemvDp4aMaxTokens = 4;
+
+// mmq_mma.cu : any m.  split_k slices of K are reduced in slice order by the last
+// block of each tile through `scratch` (fp32 partial tiles followed by tickets).
+struct MmaPlan {
+  uint32_t token_tile;   // tokens per block: 16, 32 or 64
+  uint32_t split_k;      // >= 1
+  uint32_t kbs_per_step; // super-blocks staged per shared-memory step
+};
+MmaPlan plan_mma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request);
+// partial_tiles: split_k * m * n floats; tickets: one zeroed uint32 per (row tile, token tile),
+// left zero by the kernel.  Both may be null when plan.split_k == 1.
+cudaError_t launch_mmq_mma(const WeightView& w, const Q8View& x, float* out, const float* residual,
+                           int32_t* partials, const MmaPlan& plan, void* partial_tiles,
+                           uint32_t* tickets, cudaStream_t stream);
+
+// repack.cu
+cudaError_t launch_repack_blocks144(const uint8_t* blocks, uint32_t n, uint32_t k, uint8_t* codes,
+                                    uint8_t* meta, cudaStream_t stream);
+
+}  // namespace q4k

@@ -1,0 +1,233 @@
+"""Host-side mirror of the reference's Q4_K x Q8 operator interface (cuda/q4k_q8.hpp:14-49,
+cuda/prefill.hpp:33-44) over the C ABI.  Same names, argument meaning and error behaviour;
+torch supplies device memory and streams only -- every operation is a kernel of libq4k_b200."""
+from __future__ import annotations
+
+import ctypes as C
+from dataclasses import dataclass
+from typing import Optional, Sequence
+
+import torch
+
+from . import _lib as L
+
+
+class Q4KError(RuntimeError):
+    """A rejected or failed call.  `code` is the reference's ErrorCode (cuda/error.hpp:13-17):
+    1 Status, 2 InvalidArgument, 3 Overflow."""
+
+    def __init__(self, code: int, message: str):
+        super().__init__(f"q4k error {code}: {message}")
+        self.code = code
+        self.message = message
+
+
+def _check(status: int) -> None:
+    if status != L.OK:
+        raise Q4KError(status, L.load().q4k_last_error().decode())
+
+
+def pad_n(n: int) -> int:
+    return (n + 7) // 8 * 8
+
+
+def pad_k(k: int) -> int:
+    return (k + 255) // 256 * 256
+
+
+def _stream(stream) -> C.c_void_p:
+    s = torch.cuda.current_stream() if stream is None else stream
+    return C.c_void_p(s.cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> C.c_void_p:
+    return C.c_void_p(0 if t is None else t.data_ptr())
+
+
+@dataclass
+class PrefillWeight:
+    """Q4_K matrix in split tiles (struct PrefillWeight, cuda/prefill.hpp:33-44)."""
+    codes: torch.Tensor   # uint8, padded_n * padded_k / 2 bytes
+    scales: torch.Tensor  # uint8, padded_n * (padded_k / 256) * 16 bytes
+    n: int
+    k: int
+    layout: int = L.LAYOUT_SPLIT_TILES
+    quantizer: int = L.QUANTIZER_Q4K
+    codes_bytes: Optional[int] = None    # override to build a malformed descriptor in tests
+    scales_bytes: Optional[int] = None
+
+    @property
+    def padded_n(self) -> int:
+        return pad_n(self.n)
+
+    @property
+    def padded_k(self) -> int:
+        return pad_k(self.k)
+
+    def c_struct(self) -> L.Weight:
+        return L.Weight(self.codes.data_ptr(), self.scales.data_ptr(), self.layout, self.quantizer, self.n,
+                        self.k, self.padded_n, self.padded_k,
+                        self.codes.numel() if self.codes_bytes is None else self.codes_bytes,
+                        self.scales.numel() if self.scales_bytes is None else self.scales_bytes)
+
+    @staticmethod
+    def from_host(codes, scales, n: int, k: int, device="cuda") -> "PrefillWeight":
+        """codes / scales: numpy uint8 arrays already in split-tile order."""
+        return PrefillWeight(torch.from_numpy(codes).to(device), torch.from_numpy(scales).to(device), n, k)
+
+    def nbytes(self) -> int:
+        return self.codes.numel() + self.scales.numel()
+
+    def row_slice(self, row0: int, rows: int) -> "PrefillWeight":
+        """Rows [row0, row0+rows) as a weight of its own (row0 % 8 == 0): a row group is one
+        contiguous run of tiles, so an output-row shard is a view, not a copy."""
+        if row0 % 8 != 0 or row0 + rows > self.n:
+            raise ValueError("row shard must start on a multiple of 8 inside the matrix")
+        tiles_k = self.padded_k // 256
+        g0, g1 = row0 // 8, (row0 + rows + 7) // 8
+        return PrefillWeight(self.codes[g0 * tiles_k * 1024:g1 * tiles_k * 1024],
+                             self.scales[g0 * tiles_k * 128:g1 * tiles_k * 128], rows, self.k)
+
+
+@dataclass
+class Q8Input:
+    """Quantised activations (struct Q8Input, cuda/q4k_q8.hpp:14-21)."""
+    codes: torch.Tensor   # int8  [m, padded_k]
+    scales: torch.Tensor  # fp32  [m, padded_k / 32]
+    sums: torch.Tensor    # int32 [m, padded_k / 32]
+    m: int
+    k: int
+    padded_k: int
+
+    def c_struct(self) -> L.Q8:
+        return L.Q8(self.codes.data_ptr(), self.scales.data_ptr(), self.sums.data_ptr(), self.codes.numel(),
+                    self.scales.numel(), self.sums.numel(), self.m, self.k, self.padded_k)
+
+    def rows(self, r0: int, r1: int) -> "Q8Input":
+        return Q8Input(self.codes[r0:r1], self.scales[r0:r1], self.sums[r0:r1], r1 - r0, self.k, self.padded_k)
+
+
+def new_q8_input(m: int, k: int, device="cuda") -> Q8Input:
+    pk = pad_k(k)
+    return Q8Input(torch.empty((m, pk), dtype=torch.int8, device=device),
+                   torch.empty((m, pk // 32), dtype=torch.float32, device=device),
+                   torch.empty((m, pk // 32), dtype=torch.int32, device=device), m, k, pk)
+
+
+def pack_q8(x: torch.Tensor, failure: torch.Tensor, out: Optional[Q8Input] = None, stream=None) -> Q8Input:
+    """pack_q8 (cuda/q4k_q8.hpp:32-34): bf16 (or fp32) rows [m, k] -> Q8.  `failure` is one
+    int32 on the device that the caller cleared; a non-finite group sets it to 1."""
+    lib = L.load()
+    if x.dim() != 2 or not x.is_contiguous():
+        raise Q4KError(L.ERR_INVALID_ARGUMENT, "pack_q8 takes a contiguous [m, k] tensor")
+    m, k = x.shape
+    if out is None:
+        out = new_q8_input(m, k, x.device)
+    if x.dtype == torch.bfloat16:
+        fn = lib.q4k_pack_q8_bf16
+    elif x.dtype == torch.float32:
+        fn = lib.q4k_pack_q8_f32
+    else:
+        raise Q4KError(L.ERR_INVALID_ARGUMENT, "pack_q8 takes bf16 or fp32")
+    _check(fn(_ptr(x), x.numel(), out.c_struct(), _ptr(failure), _stream(stream)))
+    return out
+
+
+def q4k_q8_project(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor] = None,
+                   residual: Optional[torch.Tensor] = None, *, kernel: int = L.KERNEL_AUTO, split_k: int = 0,
+                   partials: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                   trusted: bool = False, stream=None) -> torch.Tensor:
+    """q4k_q8_project (cuda/q4k_q8.hpp:35-37): fp32 out[token, row], token-major."""
+    lib = L.load()
+    if out is None:
+        out = torch.empty((x.m, weight.n), dtype=torch.float32, device=x.codes.device)
+    w = weight.c_struct()
+    plain = kernel == L.KERNEL_AUTO and split_k == 0 and partials is None and workspace is None and not trusted
+    if plain:
+        _check(lib.q4k_q8_project(C.byref(w), x.c_struct(), _ptr(out), out.numel(), _ptr(residual),
+                                  0 if residual is None else residual.numel(), _stream(stream)))
+    else:
+        opt = L.ProjectOptions(kernel, split_k, 0 if partials is None else partials.data_ptr(),
+                               0 if partials is None else partials.numel(),
+                               0 if workspace is None else workspace.data_ptr(),
+                               0 if workspace is None else workspace.numel() * workspace.element_size(),
+                               L.FLAG_TRUSTED_SPANS if trusted else 0)
+        _check(lib.q4k_q8_project_ex(C.byref(w), x.c_struct(), _ptr(out), out.numel(), _ptr(residual),
+                                     0 if residual is None else residual.numel(), C.byref(opt), _stream(stream)))
+    return out
+
+
+def q4k_q8_project_ragged(weight: PrefillWeight, x: Q8Input, row_offsets: Sequence[int],
+                          out: Optional[torch.Tensor] = None, *, kernel: int = L.KERNEL_AUTO,
+                          partials: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """Packed continuous batch: request r owns token rows [row_offsets[r], row_offsets[r+1])."""
+    lib = L.load()
+    if out is None:
+        out = torch.empty((x.m, weight.n), dtype=torch.float32, device=x.codes.device)
+    offs = (C.c_uint32 * len(row_offsets))(*row_offsets)
+    w = weight.c_struct()
+    opt = L.ProjectOptions(kernel, 0, 0 if partials is None else partials.data_ptr(),
+                           0 if partials is None else partials.numel(), 0, 0, 0)
+    _check(lib.q4k_q8_project_ragged(C.byref(w), x.c_struct(), offs, len(row_offsets) - 1, _ptr(out),
+                                     out.numel(), C.byref(opt), _stream(stream)))
+    return out
+
+
+def q8_mlp_workspace_bytes(m: int, hidden: int, ffn: int) -> int:
+    return L.load().q4k_q8_mlp_workspace_bytes(m, hidden, ffn)
+
+
+def q4k_q8_mlp(gate: PrefillWeight, up: PrefillWeight, down: PrefillWeight, residual: torch.Tensor,
+               gamma: torch.Tensor, eps: float, out: torch.Tensor, m: int, workspace: torch.Tensor,
+               pending_failure: Optional[torch.Tensor] = None, stream=None) -> bool:
+    """q4k_q8_mlp (cuda/q4k_q8.hpp:44-49).  Returns `submitted`; raises Q4KError on rejection
+    or, in the synchronous form (pending_failure None), on a non-finite producer."""
+    lib = L.load()
+    submitted = C.c_int(0)
+    g, u, d = gate.c_struct(), up.c_struct(), down.c_struct()
+    st = lib.q4k_q8_mlp(C.byref(g), C.byref(u), C.byref(d), _ptr(residual), _ptr(gamma), eps, _ptr(out), m,
+                        _ptr(workspace), workspace.numel() * workspace.element_size(), _stream(stream),
+                        C.byref(submitted), _ptr(pending_failure))
+    if st != L.OK:
+        err = Q4KError(st, lib.q4k_last_error().decode())
+        err.submitted = bool(submitted.value)
+        raise err
+    return bool(submitted.value)
+
+
+def hidden_rms_q8(residual: torch.Tensor, gamma: torch.Tensor, eps: float, failure: torch.Tensor,
+                  out: Optional[Q8Input] = None, stream=None) -> Q8Input:
+    """launch_hidden_rms_q8 (cuda/activation.cu:536-548)."""
+    m, hidden = residual.shape
+    if out is None:
+        out = new_q8_input(m, hidden, residual.device)
+    _check(L.load().q4k_hidden_rms_q8(_ptr(residual), _ptr(gamma), eps, m, hidden, out.c_struct(), _ptr(failure),
+                                      _stream(stream)))
+    return out
+
+
+def swiglu_pack_q8(gate: torch.Tensor, up: torch.Tensor, failure: torch.Tensor, out: Optional[Q8Input] = None,
+                   stream=None) -> Q8Input:
+    """swiglu_pack_kernel (cuda/q4k_q8.cu:52-61)."""
+    m, ffn = gate.shape
+    if out is None:
+        out = new_q8_input(m, ffn, gate.device)
+    _check(L.load().q4k_swiglu_pack_q8(_ptr(gate), _ptr(up), m, ffn, out.c_struct(), _ptr(failure), _stream(stream)))
+    return out
+
+
+def export_q8_1(x: Q8Input, stream=None) -> torch.Tensor:
+    """36-byte records {fp16 d, fp16 s, 32 codes} per K32 group."""
+    rec = torch.empty(x.scales.numel() * 36, dtype=torch.uint8, device=x.codes.device)
+    _check(L.load().q4k_export_q8_1(x.c_struct(), _ptr(rec), rec.numel(), _stream(stream)))
+    return rec
+
+
+def repack_blocks144(blocks: torch.Tensor, n: int, k: int, stream=None) -> PrefillWeight:
+    """144-byte llama.cpp-native super-blocks (device uint8) -> split tiles."""
+    pn = pad_n(n)
+    codes = torch.empty(pn * k // 2, dtype=torch.uint8, device=blocks.device)
+    scales = torch.empty(pn * (k // 256) * 16, dtype=torch.uint8, device=blocks.device)
+    _check(L.load().q4k_repack_blocks144(_ptr(blocks), blocks.numel(), n, k, _ptr(codes), codes.numel(), _ptr(scales),
+                                         scales.numel(), _stream(stream)))
+    return PrefillWeight(codes, scales, n, k)
