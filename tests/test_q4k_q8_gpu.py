@@ -203,8 +203,8 @@ def run_and_check(w: PrefillWeight, hc, hs, x_f32=None, x_bits=None, rows=None, 
         sl = slice(r0 // 8 * (pk // 256) * 1024, None)
         ref_dots = orc.dots(hc[sl], cnt, pk, rz)
         assert (part.cpu().numpy() == ref_dots).all(), "bit-exact K32 partial dots"
-        if kern != L.KERNEL_MMA:  # the slice can pick a different split-K plan than the full matrix
-            assert (ys == y[:, r0:r0 + cnt]).all()
+        # the slice may split K differently from the full matrix, so fp32 bits can differ
+        assert_close_contract(ys, y[:, r0:r0 + cnt])
     return q
 
 
