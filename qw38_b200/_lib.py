@@ -11,7 +11,7 @@ from . import build as _build
 
 OK, ERR_STATUS, ERR_INVALID_ARGUMENT, ERR_OVERFLOW = 0, 1, 2, 3
 LAYOUT_SPLIT_TILES, QUANTIZER_Q4K = 0x020D, 0x0105
-KERNEL_AUTO, KERNEL_GEMV_DP4A, KERNEL_MMA, KERNEL_TCGEN05 = 0, 1, 2, 3
+KERNEL_AUTO, KERNEL_GEMV_DP4A, KERNEL_MMA, KERNEL_TCGEN05, KERNEL_GEMV_MMA = 0, 1, 2, 3, 4
 FLAG_TRUSTED_SPANS = 1
 
 
@@ -29,7 +29,7 @@ class Q8(C.Structure):
 
 
 class ProjectOptions(C.Structure):
-    _fields_ = [("kernel", C.c_uint32), ("split_k", C.c_uint32), ("partials", C.c_void_p),
+    _fields_ = [("kernel", C.c_uint32), ("split_k", C.c_uint32), ("row_groups", C.c_uint32), ("partials", C.c_void_p),
                 ("partials_len", C.c_uint64), ("workspace", C.c_void_p),
                 ("workspace_bytes", C.c_uint64), ("flags", C.c_uint32)]
 
@@ -74,7 +74,9 @@ def load() -> C.CDLL:
     global _lib
     if _lib is not None:
         return _lib
-    path = _build.build()
+    import os
+    override = os.environ.get("Q4K_B200_LIBRARY")  # an already-built library to load instead
+    path = override if override else _build.build()
     lib = C.CDLL(str(path))
     for name, (res, args) in SIGNATURES.items():
         fn = getattr(lib, name)  # AttributeError here = header and library disagree

@@ -188,11 +188,21 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
   if (int st = check_distinct(regions, count, trusted)) return st;
 
   uint32_t kernel = opt ? opt->kernel : Q4K_KERNEL_AUTO;
-  if (kernel == Q4K_KERNEL_AUTO) kernel = x.m <= q4k::kGemvDp4aMaxTokens ? Q4K_KERNEL_GEMV_DP4A : Q4K_KERNEL_MMA;
+  if (kernel == Q4K_KERNEL_AUTO)
+    kernel = x.m <= q4k::kGemvDp4aMaxTokens ? Q4K_KERNEL_GEMV_DP4A : (x.m <= 16 ? Q4K_KERNEL_GEMV_MMA : Q4K_KERNEL_MMA);
   const float* res = residual_len ? residual : nullptr;
   if (kernel == Q4K_KERNEL_GEMV_DP4A) {
     if (x.m > q4k::kGemvDp4aMaxTokens) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: dp4a kernel takes m <= 4");
     Q4K_CUDA(q4k::launch_gemv_dp4a(view(w), view(x), output, res, partials, stream), "q4k_q8.gemv_dp4a");
+    return Q4K_OK;
+  }
+  if (kernel == Q4K_KERNEL_GEMV_MMA) {
+    if (x.m > 16) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: the cluster mma kernel takes m <= 16");
+    uint32_t const rgroups = opt ? opt->row_groups : 0, split = opt ? opt->split_k : 0;
+    if ((rgroups != 0 && rgroups != 4 && rgroups != 8) || split > 8)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: row_groups must be 4 or 8 and split_k <= 8");
+    q4k::GemvMmaPlan plan = q4k::plan_gemv_mma(x.m, w.n, w.padded_k / 256, split, rgroups);
+    Q4K_CUDA(q4k::launch_gemv_mma(view(w), view(x), output, res, partials, plan, stream), "q4k_q8.gemv_mma");
     return Q4K_OK;
   }
   if (kernel == Q4K_KERNEL_MMA) {

@@ -43,6 +43,17 @@ cudaError_t launch_mmq_mma(const WeightView& w, const Q8View& x, float* out, con
                            int32_t* partials, const MmaPlan& plan, void* partial_tiles,
                            uint32_t* tickets, cudaStream_t stream);
 
+// gemv_mma.cu : m <= 16.  K slices are the blocks of a thread-block cluster (<= 8) and are
+// added in rank order through distributed shared memory; no global scratch.
+struct GemvMmaPlan {
+  uint32_t warps;    // row groups per block: 4 or 8
+  uint32_t split_k;  // cluster size, 1..8
+};
+GemvMmaPlan plan_gemv_mma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request,
+                          uint32_t warps_request);
+cudaError_t launch_gemv_mma(const WeightView& w, const Q8View& x, float* out, const float* residual,
+                            int32_t* partials, const GemvMmaPlan& plan, cudaStream_t stream);
+
 // repack.cu
 cudaError_t launch_repack_blocks144(const uint8_t* blocks, uint32_t n, uint32_t k, uint8_t* codes,
                                     uint8_t* meta, cudaStream_t stream);

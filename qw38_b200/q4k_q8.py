@@ -135,19 +135,19 @@ def pack_q8(x: torch.Tensor, failure: torch.Tensor, out: Optional[Q8Input] = Non
 
 def q4k_q8_project(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor] = None,
                    residual: Optional[torch.Tensor] = None, *, kernel: int = L.KERNEL_AUTO, split_k: int = 0,
-                   partials: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
+                   row_groups: int = 0, partials: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
                    trusted: bool = False, stream=None) -> torch.Tensor:
     """q4k_q8_project (cuda/q4k_q8.hpp:35-37): fp32 out[token, row], token-major."""
     lib = L.load()
     if out is None:
         out = torch.empty((x.m, weight.n), dtype=torch.float32, device=x.codes.device)
     w = weight.c_struct()
-    plain = kernel == L.KERNEL_AUTO and split_k == 0 and partials is None and workspace is None and not trusted
+    plain = kernel == L.KERNEL_AUTO and split_k == 0 and row_groups == 0 and partials is None and workspace is None and not trusted
     if plain:
         _check(lib.q4k_q8_project(C.byref(w), x.c_struct(), _ptr(out), out.numel(), _ptr(residual),
                                   0 if residual is None else residual.numel(), _stream(stream)))
     else:
-        opt = L.ProjectOptions(kernel, split_k, 0 if partials is None else partials.data_ptr(),
+        opt = L.ProjectOptions(kernel, split_k, row_groups, 0 if partials is None else partials.data_ptr(),
                                0 if partials is None else partials.numel(),
                                0 if workspace is None else workspace.data_ptr(),
                                0 if workspace is None else workspace.numel() * workspace.element_size(),
@@ -166,7 +166,7 @@ def q4k_q8_project_ragged(weight: PrefillWeight, x: Q8Input, row_offsets: Sequen
         out = torch.empty((x.m, weight.n), dtype=torch.float32, device=x.codes.device)
     offs = (C.c_uint32 * len(row_offsets))(*row_offsets)
     w = weight.c_struct()
-    opt = L.ProjectOptions(kernel, 0, 0 if partials is None else partials.data_ptr(),
+    opt = L.ProjectOptions(kernel, 0, 0, 0 if partials is None else partials.data_ptr(),
                            0 if partials is None else partials.numel(), 0, 0, 0)
     _check(lib.q4k_q8_project_ragged(C.byref(w), x.c_struct(), offs, len(row_offsets) - 1, _ptr(out),
                                      out.numel(), C.byref(opt), _stream(stream)))

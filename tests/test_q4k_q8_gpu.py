@@ -44,7 +44,7 @@ def fixture_a(golden):
 
 
 def kernels_for(m):
-    return ([L.KERNEL_GEMV_DP4A] if m <= 4 else []) + [L.KERNEL_MMA]
+    return ([L.KERNEL_GEMV_DP4A] if m <= 4 else []) + ([L.KERNEL_GEMV_MMA] if m <= 16 else []) + [L.KERNEL_MMA]
 
 
 SMALL_TILE = {}
@@ -215,7 +215,7 @@ def test_config0_single_gemv():
     assert hc.size + hs.size == 50135040
     w = PrefillWeight.from_host(hc, hs, 17408, 5120)
     x = synth.activations(1, 5120, seed=0)
-    run_and_check(w, hc, hs, x_f32=x, kernels=[L.KERNEL_AUTO, L.KERNEL_GEMV_DP4A, L.KERNEL_MMA])
+    run_and_check(w, hc, hs, x_f32=x, kernels=[L.KERNEL_AUTO, L.KERNEL_GEMV_DP4A, L.KERNEL_GEMV_MMA, L.KERNEL_MMA])
 
 
 @pytest.mark.parametrize("m", [1, 2, 4, 8, 16])
@@ -226,7 +226,7 @@ def test_config1_decode_projection_set(name, n, k, m):
     hc, hs = w.codes.cpu().numpy(), w.scales.cpu().numpy()
     xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=m))
     sample = [(0, 64), (n // 2 + 8, 40), (n - 72, 72)]
-    kernels = [L.KERNEL_AUTO] + ([L.KERNEL_MMA] if m <= 4 else [])
+    kernels = [L.KERNEL_AUTO, L.KERNEL_GEMV_MMA] + ([L.KERNEL_MMA] if m <= 4 else [])
     run_and_check(w, hc, hs, x_bits=xb, rows=sample, kernels=kernels, partial_rows=128)
 
 
@@ -263,6 +263,33 @@ def test_split_k_is_deterministic_and_exact(split_k):
         assert (mine == y).all()
         with pytest.raises(Q4KError):
             q4k_q8_project(w, q, kernel=L.KERNEL_MMA, split_k=split_k, workspace=ws[: ws_bytes // 2])
+
+
+@pytest.mark.parametrize("m", [3, 8, 9, 16])
+@pytest.mark.parametrize("split_k,row_groups", [(1, 4), (2, 8), (3, 4), (5, 8), (8, 4)])
+def test_cluster_split_k_is_deterministic_and_exact(m, split_k, row_groups):
+    """K slices inside a thread-block cluster, added in rank order through distributed shared memory."""
+    n, k = 1000, 5120                     # n % 64 != 0: inactive warps and a ragged last row group
+    codes, meta = synth.logical_q4k(n, k, seed=6)
+    hc, hs = synth.split_tiles(codes, meta)
+    w = PrefillWeight.from_host(hc, hs, n, k)
+    xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=m))
+    q = pack_q8(bf16_tensor(xb), flag())
+    rz, ra, rs, _ = orc.q8_quantize(xb, bf16_bits=True)
+    ref = orc.project(hc, hs, n, k, rz, ra, rs)
+    part = torch.empty((m, n, 160), dtype=torch.int32, device=DEV)
+    res = dev(synth.activations(m, n, seed=4))
+    guarded = torch.full((m * n + 2,), -5.0, dtype=torch.float32, device=DEV)
+    y = q4k_q8_project(w, q, out=guarded[1:-1].view(m, n), kernel=L.KERNEL_GEMV_MMA, split_k=split_k,
+                       row_groups=row_groups, partials=part, residual=res).cpu().numpy()
+    assert guarded[0].item() == -5.0 and guarded[-1].item() == -5.0
+    assert_close_contract(y - res.cpu().numpy(), ref)
+    assert (part.cpu().numpy() == orc.dots(hc, n, k, rz)).all()
+    for _ in range(2):
+        again = q4k_q8_project(w, q, kernel=L.KERNEL_GEMV_MMA, split_k=split_k, row_groups=row_groups, residual=res)
+        assert (again.cpu().numpy() == y).all()
+    with pytest.raises(Q4KError):
+        q4k_q8_project(w, q, kernel=L.KERNEL_GEMV_MMA, split_k=9)
 
 
 def ragged_offsets():
