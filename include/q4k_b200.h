@@ -91,6 +91,12 @@ const char* q4k_last_error(void);   /* thread-local text of the last failure */
 int q4k_last_cuda_status(void);     /* cudaError_t of the last Q4K_ERR_STATUS */
 uint32_t q4k_abi_version(void);
 
+/* Synchronises the current device and reads the status word of the tcgen05 kernel (library-owned
+ * scratch): 0 = every launch so far ran to completion; nonzero = a bounded wait inside the
+ * kernel gave up at that site and the affected block returned without writing its outputs.
+ * No counterpart in the reference, whose kernels have no device-side waits. */
+int q4k_kernel_status(int* value);
+
 /* Padding rules (decode_pad_n / decode_pad_k / decode_code_bytes / decode_scale_bytes,
  * cuda/decode_mmv.hpp:148-205, Q4_K branch). */
 uint64_t q4k_pad_n(uint32_t n);

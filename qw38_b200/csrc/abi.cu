@@ -189,7 +189,10 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
 
   uint32_t kernel = opt ? opt->kernel : Q4K_KERNEL_AUTO;
   if (kernel == Q4K_KERNEL_AUTO)
-    kernel = x.m <= q4k::kGemvDp4aMaxTokens ? Q4K_KERNEL_GEMV_DP4A : (x.m <= 16 ? Q4K_KERNEL_GEMV_MMA : Q4K_KERNEL_MMA);
+    kernel = x.m <= q4k::kGemvDp4aMaxTokens
+                 ? Q4K_KERNEL_GEMV_DP4A
+                 : (x.m <= 16 ? Q4K_KERNEL_GEMV_MMA
+                              : (q4k::tcgen05_supported(view(w), view(x)) ? Q4K_KERNEL_TCGEN05 : Q4K_KERNEL_MMA));
   const float* res = residual_len ? residual : nullptr;
   if (kernel == Q4K_KERNEL_GEMV_DP4A) {
     if (x.m > q4k::kGemvDp4aMaxTokens) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: dp4a kernel takes m <= 4");
@@ -203,6 +206,30 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
       return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: row_groups must be 4 or 8 and split_k <= 8");
     q4k::GemvMmaPlan plan = q4k::plan_gemv_mma(x.m, w.n, w.padded_k / 256, split, rgroups);
     Q4K_CUDA(q4k::launch_gemv_mma(view(w), view(x), output, res, partials, plan, stream), "q4k_q8.gemv_mma");
+    return Q4K_OK;
+  }
+  if (kernel == Q4K_KERNEL_TCGEN05) {
+    if (!q4k::tcgen05_supported(view(w), view(x)))
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: the tcgen05 kernel needs 16-byte aligned operands");
+    q4k::TcPlan plan = q4k::plan_tcgen05(x.m, w.n, w.padded_k / 256, opt ? opt->split_k : 0);
+    uint64_t const tiles = uint64_t((w.padded_n + 127) / 128) * ((x.m + plan.ntok - 1) / plan.ntok);
+    if (plan.split_k > 1 && tiles * 4 > kTicketRegion - 64)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: too many tiles for split-K");
+    uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
+    void* scratch = nullptr;
+    if (opt && opt->workspace) {
+      if (opt->workspace_bytes < kTicketRegion + partial_bytes)
+        return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: workspace too small");
+      scratch = opt->workspace;
+      Q4K_CUDA(cudaMemsetAsync(scratch, 0, kTicketRegion, stream), "q4k_q8.clear_tickets");
+    } else if (int st = own_scratch(partial_bytes, &scratch)) {
+      return st;
+    }
+    int* status = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch) + kTicketRegion - 4);
+    Q4K_CUDA(q4k::launch_mmq_tcgen05(view(w), view(x), output, res, partials, plan,
+                                     static_cast<uint8_t*>(scratch) + kTicketRegion, static_cast<uint32_t*>(scratch),
+                                     status, stream),
+             "q4k_q8.mmq_tcgen05");
     return Q4K_OK;
   }
   if (kernel == Q4K_KERNEL_MMA) {
@@ -263,6 +290,22 @@ uint64_t q4k_pad_n(uint32_t n) { return n == 0 ? 0 : (uint64_t(n) + 7) / 8 * 8; 
 uint32_t q4k_pad_k(uint32_t k) { return k == 0 ? 0 : (k + 255u) / 256u * 256u; }
 uint64_t q4k_code_bytes(uint32_t padded_n, uint32_t padded_k) { return uint64_t(padded_n) * padded_k / 2; }
 uint64_t q4k_scale_bytes(uint32_t padded_n, uint32_t padded_k) { return uint64_t(padded_n) * (padded_k / 256) * 16; }
+
+int q4k_kernel_status(int* value) {
+  if (!value) return fail(Q4K_ERR_INVALID_ARGUMENT, "kernel_status: null output");
+  *value = 0;
+  int device = 0;
+  Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+  void* p = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (device >= 0 && device < 64) p = g_scratch[device].p;
+  }
+  if (!p) return Q4K_OK;  // nothing has used the library-owned scratch yet
+  Q4K_CUDA(cudaDeviceSynchronize(), "kernel_status.sync");
+  Q4K_CUDA(cudaMemcpy(value, static_cast<uint8_t*>(p) + kTicketRegion - 4, 4, cudaMemcpyDeviceToHost), "kernel_status.read");
+  return Q4K_OK;
+}
 
 int q4k_validate_device_span(const void* pointer, uint64_t bytes, uint32_t alignment, int device) {
   return check_span(Region{pointer, bytes, alignment, "span"}, device);

@@ -54,6 +54,18 @@ GemvMmaPlan plan_gemv_mma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
 cudaError_t launch_gemv_mma(const WeightView& w, const Q8View& x, float* out, const float* residual,
                             int32_t* partials, const GemvMmaPlan& plan, cudaStream_t stream);
 
+// mmq_tcgen05.cu : tcgen05 kind::i8 with TMEM accumulators, 128 rows x {16,32,64,128} tokens
+// per block.  status receives a nonzero site code if a bounded wait inside the kernel gave up.
+struct TcPlan {
+  uint32_t ntok;
+  uint32_t split_k;
+};
+bool tcgen05_supported(const WeightView& w, const Q8View& x);
+TcPlan plan_tcgen05(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request);
+cudaError_t launch_mmq_tcgen05(const WeightView& w, const Q8View& x, float* out, const float* residual,
+                               int32_t* partials, const TcPlan& plan, void* partial_tiles, uint32_t* tickets,
+                               int* status, cudaStream_t stream);
+
 // repack.cu
 cudaError_t launch_repack_blocks144(const uint8_t* blocks, uint32_t n, uint32_t k, uint8_t* codes,
                                     uint8_t* meta, cudaStream_t stream);

@@ -44,7 +44,15 @@ def fixture_a(golden):
 
 
 def kernels_for(m):
-    return ([L.KERNEL_GEMV_DP4A] if m <= 4 else []) + ([L.KERNEL_GEMV_MMA] if m <= 16 else []) + [L.KERNEL_MMA]
+    return (([L.KERNEL_GEMV_DP4A] if m <= 4 else []) + ([L.KERNEL_GEMV_MMA] if m <= 16 else []) +
+            [L.KERNEL_MMA, L.KERNEL_TCGEN05])
+
+
+def kernel_status() -> int:
+    import ctypes
+    v = ctypes.c_int(-1)
+    assert L.load().q4k_kernel_status(ctypes.byref(v)) == 0
+    return v.value
 
 
 SMALL_TILE = {}
@@ -85,7 +93,9 @@ def test_reference_case(fixture_a, m):
         shifted_z = torch.full((pk + 8,), 99, dtype=torch.int8, device=DEV)
         shifted_z[4:-4] = q.codes[0]
         residual = dev(((np.arange(n) % 17) - 8).astype(np.float32) * 0.125)
-        for kern in kernels_for(1):
+        with pytest.raises(Q4KError):   # TMA needs 16-byte aligned operands: a clear rejection, not a fault
+            q4k_q8_project(PrefillWeight(shifted_w[4:-4], w.scales, n, k), q, kernel=L.KERNEL_TCGEN05)
+        for kern in [kk for kk in kernels_for(1) if kk != L.KERNEL_TCGEN05]:
             base = q4k_q8_project(w, q, kernel=kern).cpu().numpy()[0]
             for variant in range(8):
                 ww = PrefillWeight(shifted_w[4:-4] if variant & 1 else w.codes,
@@ -102,6 +112,7 @@ def test_reference_case(fixture_a, m):
         assert (y[:127] == SMALL_TILE["y"]).all(), "rows do not depend on the token count"
     y2 = q4k_q8_project(w, q).cpu().numpy()
     assert (y2 == y).all(), "reused pack gives identical output"
+    assert kernel_status() == 0, "no bounded wait inside a kernel gave up"
     z2, a2, s2 = host_q8(q)
     assert (z2 == z).all() and (a2.view(np.uint32) == a.view(np.uint32)).all() and (s2 == s).all(), "consumer preserves the pack"
     bad = Q8Input(q.codes.view(-1)[:1], q.scales, q.sums, m, k, pk)
@@ -226,7 +237,7 @@ def test_config1_decode_projection_set(name, n, k, m):
     hc, hs = w.codes.cpu().numpy(), w.scales.cpu().numpy()
     xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=m))
     sample = [(0, 64), (n // 2 + 8, 40), (n - 72, 72)]
-    kernels = [L.KERNEL_AUTO, L.KERNEL_GEMV_MMA] + ([L.KERNEL_MMA] if m <= 4 else [])
+    kernels = [L.KERNEL_AUTO, L.KERNEL_GEMV_MMA, L.KERNEL_TCGEN05] + ([L.KERNEL_MMA] if m <= 4 else [])
     run_and_check(w, hc, hs, x_bits=xb, rows=sample, kernels=kernels, partial_rows=128)
 
 
@@ -236,11 +247,14 @@ def test_config2_prefill_shapes_sampled(m, n, k):
     w = synth.device_weight(n, k, seed=7)
     hc, hs = w.codes.cpu().numpy(), w.scales.cpu().numpy()
     xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=2, scale=0.5, outlier_frac=0.01))
-    run_and_check(w, hc, hs, x_bits=xb, rows=[(8, 24), (n - 16, 16)], partial_rows=16)
+    run_and_check(w, hc, hs, x_bits=xb, rows=[(8, 24), (n - 16, 16)], kernels=[L.KERNEL_AUTO, L.KERNEL_TCGEN05, L.KERNEL_MMA],
+                  partial_rows=16)
+    assert kernel_status() == 0
 
 
+@pytest.mark.parametrize("kern", [L.KERNEL_MMA, L.KERNEL_TCGEN05])
 @pytest.mark.parametrize("split_k", [1, 2, 3, 5, 20])
-def test_split_k_is_deterministic_and_exact(split_k):
+def test_split_k_is_deterministic_and_exact(split_k, kern):
     n, k, m = 640, 5120, 16
     w = synth.device_weight(n, k, seed=5)
     hc, hs = w.codes.cpu().numpy(), w.scales.cpu().numpy()
@@ -250,19 +264,19 @@ def test_split_k_is_deterministic_and_exact(split_k):
     ref = orc.project(hc, hs, n, 5120, rz, ra, rs)
     part = torch.empty((m, n, 160), dtype=torch.int32, device=DEV)
     res = dev(synth.activations(m, n, seed=4))
-    y = q4k_q8_project(w, q, kernel=L.KERNEL_MMA, split_k=split_k, partials=part, residual=res).cpu().numpy()
+    y = q4k_q8_project(w, q, kernel=kern, split_k=split_k, partials=part, residual=res).cpu().numpy()
     assert_close_contract(y - res.cpu().numpy(), ref)
     assert (part.cpu().numpy() == orc.dots(hc, n, 5120, rz)).all()
     for _ in range(3):
-        again = q4k_q8_project(w, q, kernel=L.KERNEL_MMA, split_k=split_k, residual=res).cpu().numpy()
+        again = q4k_q8_project(w, q, kernel=kern, split_k=split_k, residual=res).cpu().numpy()
         assert (again == y).all(), "slice sums are added in slice order, whatever the arrival order"
     ws_bytes = L.load().q4k_project_workspace_bytes(m, n, split_k)
     if ws_bytes:
         ws = torch.full((ws_bytes,), 0xAB, dtype=torch.uint8, device=DEV)   # dirty caller workspace
-        mine = q4k_q8_project(w, q, kernel=L.KERNEL_MMA, split_k=split_k, residual=res, workspace=ws).cpu().numpy()
+        mine = q4k_q8_project(w, q, kernel=kern, split_k=split_k, residual=res, workspace=ws).cpu().numpy()
         assert (mine == y).all()
         with pytest.raises(Q4KError):
-            q4k_q8_project(w, q, kernel=L.KERNEL_MMA, split_k=split_k, workspace=ws[: ws_bytes // 2])
+            q4k_q8_project(w, q, kernel=kern, split_k=split_k, workspace=ws[: ws_bytes // 2])
 
 
 @pytest.mark.parametrize("m", [3, 8, 9, 16])
