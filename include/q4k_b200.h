@@ -136,6 +136,25 @@ int q4k_q8_project_ex(const q4k_weight* weight, q4k_q8_input input, float* outpu
 /* Scratch bytes q4k_q8_project_ex needs for (m, n, split_k); 0 when split_k <= 1. */
 uint64_t q4k_project_workspace_bytes(uint32_t m, uint32_t n, uint32_t split_k);
 
+/* The same projection for callers that must never allocate device memory -- a serving process
+ * whose own arena owns the whole GPU, a latency-critical stream that cannot afford the implicit
+ * synchronisation of an allocation, a host with allocator hooks that reject foreign requests.
+ * It runs the split-K warp-MMA kernel (Q4K_KERNEL_MMA) with its scratch in a fixed array inside
+ * the library image instead of a lazily allocated buffer: no cudaMalloc, no cudaFree, no
+ * allocating library routine, on any call.  Limits: split_k * m * n * 4 <= Q4K_STATIC_SCRATCH_BYTES
+ * and at most 4096 output tiles when split_k > 1; larger requests are rejected with
+ * Q4K_ERR_INVALID_ARGUMENT and a message naming the limit.  The array costs that much device
+ * memory (plus 16 KiB) on every GPU that loads the library, until the process exits.
+ * The first call on a device looks up the array's device address; make that call before any
+ * stream capture on that device.  All calls on a device share the one array, which keeps the
+ * previous call's contents: the arrival counters are cleared at the start of each call, and
+ * two calls whose kernels overlap on the GPU (different streams) race on it -- serialise them.
+ * This entry point has no counterpart in the reference. */
+#define Q4K_STATIC_SCRATCH_BYTES (8ull * 1024 * 1024)
+int q4k_q8_project_static(const q4k_weight* weight, q4k_q8_input input, float* output,
+                          uint64_t output_len, const float* residual, uint64_t residual_len,
+                          uint32_t split_k, void* stream);
+
 /* Ragged continuous batch: requests r = 0..n_requests-1 own the packed token rows
  * [row_offsets[r], row_offsets[r+1]) of one Q8 pack with m = row_offsets[n_requests].
  * The projection is row independent and position free (cuda/prefill.hpp:58-60), so

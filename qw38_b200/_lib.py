@@ -53,6 +53,7 @@ SIGNATURES = {
     "q4k_export_q8_1": (_i, [Q8, _vp, _u64, _vp]),
     "q4k_q8_project": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _vp]),
     "q4k_q8_project_ex": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _OP, _vp]),
+    "q4k_q8_project_static": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _u32, _vp]),
     "q4k_project_workspace_bytes": (_u64, [_u32, _u32, _u32]),
     "q4k_q8_project_ragged": (_i, [_WP, Q8, C.POINTER(_u32), _u32, _vp, _u64, _OP, _vp]),
     "q4k_repack_blocks144": (_i, [_vp, _u64, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),

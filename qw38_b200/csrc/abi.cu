@@ -280,6 +280,17 @@ int pack_impl(const void* input, bool fp32, uint64_t input_len, const q4k_q8_inp
 
 }  // namespace
 
+namespace q4k {
+int set_error(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof g_error, fmt, ap);
+  va_end(ap);
+  return code;
+}
+int set_error_cuda(cudaError_t status, const char* operation) { return fail_cuda(status, operation); }
+}  // namespace q4k
+
 extern "C" {
 
 const char* q4k_last_error(void) { return g_error; }

@@ -66,6 +66,10 @@ cudaError_t launch_mmq_tcgen05(const WeightView& w, const Q8View& x, float* out,
                                int32_t* partials, const TcPlan& plan, void* partial_tiles, uint32_t* tickets,
                                int* status, cudaStream_t stream);
 
+// abi.cu : records the thread-local error text behind q4k_last_error() and returns `code`.
+int set_error(int code, const char* fmt, ...);
+int set_error_cuda(cudaError_t status, const char* operation);
+
 // repack.cu
 cudaError_t launch_repack_blocks144(const uint8_t* blocks, uint32_t n, uint32_t k, uint8_t* codes,
                                     uint8_t* meta, cudaStream_t stream);

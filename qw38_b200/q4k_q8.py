@@ -157,6 +157,20 @@ def q4k_q8_project(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor
     return out
 
 
+def q4k_q8_project_static(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor] = None,
+                          residual: Optional[torch.Tensor] = None, *, split_k: int = 0, stream=None) -> torch.Tensor:
+    """The projection for callers that may not allocate device memory: split-K scratch lives in a
+    fixed array inside the library (8 MiB), so the call never reaches cudaMalloc.  `out` must be
+    supplied by such callers; it is created here only as a convenience for tests."""
+    lib = L.load()
+    if out is None:
+        out = torch.empty((x.m, weight.n), dtype=torch.float32, device=x.codes.device)
+    w = weight.c_struct()
+    _check(lib.q4k_q8_project_static(C.byref(w), x.c_struct(), _ptr(out), out.numel(), _ptr(residual),
+                                     0 if residual is None else residual.numel(), split_k, _stream(stream)))
+    return out
+
+
 def q4k_q8_project_ragged(weight: PrefillWeight, x: Q8Input, row_offsets: Sequence[int],
                           out: Optional[torch.Tensor] = None, *, kernel: int = L.KERNEL_AUTO,
                           partials: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
