@@ -213,7 +213,7 @@ def main():
                 raise SystemExit(f"{n} rows do not split evenly over {world} ranks in row groups of 8")
             outs[(m, i)] = torch.empty((m, rows), dtype=torch.float32, device=dev)
             if world > 1:  # rank g's slice lands in gathered[g]; out[t, g*per + j] = gathered[g, t, j]
-                gathered[(m, i)] = torch.empty((world, m, per), dtype=torch.float32, device=dev)
+                gathered[(m, i)] = torch.empty((world * m, per), dtype=torch.float32, device=dev)
 
     launches = {"n": 0}
 

@@ -1,0 +1,25 @@
+"""Output-row sharding of a Q4_K matrix over the ranks of one node.
+
+Rows are independent (out[row] depends on W[row, :] and x only), so each rank keeps a contiguous
+run of row groups (8 rows, the unit of the split-tile layout), quantises the replicated
+activations itself, and the [m, rows] output slices are all-gathered.  No other exchange."""
+from __future__ import annotations
+
+from typing import Tuple
+
+
+def row_shard(n: int, world: int, rank: int) -> Tuple[int, int, int]:
+    """(first row, rows, rows per full shard) of `rank`.  Shards are multiples of 8 rows; the
+    last ranks may hold fewer rows (or none) when n/8 does not divide evenly."""
+    if world < 1 or not (0 <= rank < world):
+        raise ValueError("rank outside the world")
+    per = (((n + 7) // 8) + world - 1) // world * 8
+    row0 = min(n, rank * per)
+    return row0, min(n, row0 + per) - row0, per
+
+
+def gathered_to_token_major(gathered, n: int):
+    """gathered: [world, m, per] as written by all_gather_into_tensor (rank g's slice in
+    gathered[g]).  Returns the [m, n] token-major view-or-copy: out[t, g*per + j] = gathered[g, t, j]."""
+    world, m, per = gathered.shape
+    return gathered.permute(1, 0, 2).reshape(m, world * per)[:, :n]
