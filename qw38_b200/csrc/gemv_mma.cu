@@ -32,6 +32,8 @@ constexpr int kStages = 3;
 constexpr int kStageBytes = 1024 + 128;
 constexpr int kStep = 4;            // super-blocks of activations staged at a time
 constexpr int kActRow = 256 + 32;   // bytes per token per super-block; 32 mod 128 keeps LDS.64 conflict-free
+constexpr uint32_t kMagicI = 0x4B400000u;  // bit pattern of 1.5 * 2^23
+constexpr float kMagicF = 12582912.0f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -89,8 +91,10 @@ __device__ __forceinline__ void fill_stage(uint8_t* stage, const uint8_t* codes,
 template <int Warps, int Tokens> struct Smem {
   static constexpr int kRing = Warps * kStages * kStageBytes;
   static constexpr int kTab = Warps * 8 * 4 * 16;            // [warp][group][row pair] float4
-  static constexpr int kAct = kStep * Tokens * kActRow;      // [kbl][token][288]
-  static constexpr int kAf = kStep * 8 * Tokens * 16;        // [kbl*8+g][token] (a, a, fs, fs)
+  static constexpr int kAct1 = kStep * Tokens * kActRow;     // [kbl][token][288]
+  static constexpr int kAf1 = kStep * 8 * Tokens * 16;       // [kbl*8+g][token] (a, a, fs, fs)
+  static constexpr int kAct = 2 * kAct1;                     // double buffered
+  static constexpr int kAf = 2 * kAf1;
   static constexpr int kRed = Warps * 32 * 16;               // [warp][lane] float4 slice sums
   static constexpr int kTotal = kRing + kTab + kAct + kAf + kRed;
 };
@@ -127,81 +131,139 @@ __global__ void __launch_bounds__(Warps * 32) gemv_mma_kernel(WeightView w, Q8Vi
 
   float2 acc_lo = make_float2(0.f, 0.f), acc_hi = make_float2(0.f, 0.f);  // tokens tq / tq+8, rows 2c, 2c+1
 
-  uint32_t next_load = kb0;
-#pragma unroll
-  for (int s = 0; s < kStages - 1; ++s) {
-    if (active && next_load < kb1)
-      fill_stage<Wide>(ring + (next_load - kb0) % kStages * kStageBytes, cbase + uint64_t(next_load) * 1024,
-                       mbase + uint64_t(next_load) * 128, lane);
+  // Weight pipeline.  Everything that does not change from tile to tile is computed once:
+  // the lane's two source offsets, its swizzled destination offsets, running pointers and a
+  // stage counter (no per-tile multiply or modulo).
+  uint32_t const q0 = lane, q1 = lane + 32;
+  uint32_t const dst0 = (q0 >> 3) * 128 + (((q0 & 7) ^ (q0 >> 3)) << 4), dst1 = (q1 >> 3) * 128 + (((q1 & 7) ^ (q1 >> 3)) << 4);
+  uint32_t const ring_s = smem_u32(ring);
+  const uint8_t* cptr = cbase + uint64_t(kb0) * 1024;
+  const uint8_t* mptr = mbase + uint64_t(kb0) * 128;
+  uint32_t next_load = kb0, load_stage = 0;
+  auto issue = [&]() {
+    if (active && next_load < kb1) {
+      if constexpr (Wide) {
+        uint32_t const sb = ring_s + load_stage * kStageBytes;
+        cp_async16(sb + dst0, cptr + q0 * 16);
+        cp_async16(sb + dst1, cptr + q1 * 16);
+        if (lane < 8) cp_async16(sb + 1024 + lane * 16, mptr + lane * 16);
+      } else {
+        fill_stage<false>(ring + load_stage * kStageBytes, cptr, mptr, lane);
+      }
+    }
+    cptr += 1024;
+    mptr += 128;
     ++next_load;
+    if (++load_stage == kStages) load_stage = 0;
     cp_async_commit();
-  }
+  };
+#pragma unroll
+  for (int s = 0; s < kStages - 1; ++s) issue();
 
   bool const act16 = (reinterpret_cast<uintptr_t>(x.codes) & 15) == 0;
   // lane-constant shared addresses
-  const uint8_t* const act_lane = act + tq * kActRow + c * 8;
-  const uint8_t* const af_lane = af + tq * 16;
-  const uint8_t* const tab_lane = tab + c * 16;
   uint32_t const ldm_row = lane & 7, ldm_mat = lane >> 3;
+  uint32_t const ldm_off0 = ldm_row * 128 + ((ldm_mat ^ ldm_row) << 4), ldm_off1 = ldm_row * 128 + (((ldm_mat + 4) ^ ldm_row) << 4);
+  const uint8_t* const tab_lane = tab + c * 16;
+  float* const tab_wa = reinterpret_cast<float*>(tab + c * 64 + (tq >> 1) * 16) + (tq & 1);
+  float* const tab_wb = reinterpret_cast<float*>(tab + (c + 4) * 64 + (tq >> 1) * 16) + (tq & 1);
+  float2 const nmagic2 = make_float2(-kMagicF, -kMagicF);
 
-  for (uint32_t step0 = kb0; step0 < kb1; step0 += kStep) {
-    uint32_t const kbs = min(uint32_t(kStep), kb1 - step0);
-    __syncthreads();
-    // Stage activations: thread (token, l16) moves the 16-byte chunks l16 of each super-block.
-    for (uint32_t t = threadIdx.x >> 4; t < Tokens; t += kThreads / 16) {
-      uint32_t const l16 = threadIdx.x & 15;
-      bool const live = t < x.m;
-      const uint8_t* src = reinterpret_cast<const uint8_t*>(x.codes) + uint64_t(live ? t : 0) * pk + uint64_t(step0) * 256 + l16 * 16;
-      for (uint32_t kbl = 0; kbl < kbs; ++kbl) {
+  // Activation staging: the global loads of the next step are issued into registers before the
+  // current step is computed and stored (de-interleaved) into the other buffer afterwards.
+  constexpr int kTpt = (Tokens * 16 + kThreads - 1) / kThreads;  // tokens per thread
+  uint32_t const l16 = threadIdx.x & 15;
+  uint4 sz[kTpt][kStep];
+  float sa[kTpt][2];
+  int ss[kTpt][2];
+  auto stage_load = [&](uint32_t s0, uint32_t kbs) {
+#pragma unroll
+    for (int tt = 0; tt < kTpt; ++tt) {
+      uint32_t const t = (threadIdx.x >> 4) + tt * (kThreads / 16);
+      bool const live = t < Tokens && t < x.m;
+      const uint8_t* src = reinterpret_cast<const uint8_t*>(x.codes) + uint64_t(live ? t : 0) * pk + uint64_t(s0) * 256 + l16 * 16;
+#pragma unroll
+      for (int kbl = 0; kbl < kStep; ++kbl) {
         uint4 z = make_uint4(0, 0, 0, 0);
-        if (live) {
+        if (live && uint32_t(kbl) < kbs) {
           if (act16) z = __ldg(reinterpret_cast<const uint4*>(src + kbl * 256));
           else {
             const uint32_t* s32 = reinterpret_cast<const uint32_t*>(src + kbl * 256);
             z = make_uint4(__ldg(s32), __ldg(s32 + 1), __ldg(s32 + 2), __ldg(s32 + 3));
           }
         }
-        *reinterpret_cast<uint4*>(act + (kbl * Tokens + t) * kActRow + l16 * 16) =
-            make_uint4(even_bytes(z.x, z.y), odd_bytes(z.x, z.y), even_bytes(z.z, z.w), odd_bytes(z.z, z.w));
+        sz[tt][kbl] = z;
       }
-      for (uint32_t j = l16; j < kbs * 8; j += 16) {
-        float a = 0.f, fs = 0.f;
-        if (live) {
-          uint64_t const gi = uint64_t(t) * G + step0 * 8 + j;
-          a = __ldg(x.scales + gi);
-          fs = float(__ldg(x.sums + gi));
-        }
-        *reinterpret_cast<float4*>(af + (j * Tokens + t) * 16) = make_float4(a, a, fs, fs);
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        uint32_t const j = l16 + 16 * jj;
+        bool const ok = live && j < kbs * 8;
+        uint64_t const gi = uint64_t(live ? t : 0) * G + s0 * 8 + (ok ? j : 0);
+        sa[tt][jj] = ok ? __ldg(x.scales + gi) : 0.f;
+        ss[tt][jj] = ok ? __ldg(x.sums + gi) : 0;
       }
     }
-    __syncthreads();
+  };
+  auto stage_store = [&](uint32_t buf) {
+    uint8_t* const ab = act + buf * S::kAct1;
+    uint8_t* const fb = af + buf * S::kAf1;
+#pragma unroll
+    for (int tt = 0; tt < kTpt; ++tt) {
+      uint32_t const t = (threadIdx.x >> 4) + tt * (kThreads / 16);
+      if (t >= Tokens) continue;
+#pragma unroll
+      for (int kbl = 0; kbl < kStep; ++kbl) {
+        uint4 const z = sz[tt][kbl];
+        *reinterpret_cast<uint4*>(ab + (kbl * Tokens + t) * kActRow + l16 * 16) =
+            make_uint4(even_bytes(z.x, z.y), odd_bytes(z.x, z.y), even_bytes(z.z, z.w), odd_bytes(z.z, z.w));
+      }
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        float const a = sa[tt][jj], fs = float(ss[tt][jj]);
+        *reinterpret_cast<float4*>(fb + ((l16 + 16 * jj) * Tokens + t) * 16) = make_float4(a, a, fs, fs);
+      }
+    }
+  };
+
+  uint32_t cur = 0, use_stage = 0;
+  stage_load(kb0, min(uint32_t(kStep), kb1 - kb0));
+  stage_store(0);
+  __syncthreads();
+  for (uint32_t step0 = kb0; step0 < kb1; step0 += kStep) {
+    uint32_t const kbs = min(uint32_t(kStep), kb1 - step0);
+    uint32_t const next0 = step0 + kStep;
+    bool const has_next = next0 < kb1;
+    if (has_next) stage_load(next0, min(uint32_t(kStep), kb1 - next0));
 
     if (active) {
+      const uint8_t* const act_lane = act + cur * S::kAct1 + tq * kActRow + c * 8;
+      const uint8_t* const af_lane = af + cur * S::kAf1 + tq * 16;
       for (uint32_t kbl = 0; kbl < kbs; ++kbl) {
         uint32_t const kb = step0 + kbl;
         cp_async_wait<kStages - 2>();
         __syncwarp();
-        uint8_t* const stage = ring + (kb - kb0) % kStages * kStageBytes;
+        uint8_t* const stage = ring + use_stage * kStageBytes;
+        if (++use_stage == kStages) use_stage = 0;
         {
           // lane (r = tq, c): groups c and c+4 of row r -> table[g][r/2] = (D, D', -Mn, -Mn')
           uint4 const cm = *reinterpret_cast<const uint4*>(stage + 1024 + tq * 16);
           float const d = fp16_bits_to_f32(cm.x & 0xffffu), ndmin = -fp16_bits_to_f32(cm.x >> 16);
           uint32_t const sh = c * 8;
           uint32_t const x0 = cm.y >> sh, x1 = cm.z >> sh, x2 = cm.w >> sh;
-          float const sc_a = float(x0 & 63u), mn_a = float(x1 & 63u);
-          float const sc_b = float((x2 & 15u) | ((x0 >> 2) & 0x30u)), mn_b = float(((x2 >> 4) & 15u) | ((x1 >> 2) & 0x30u));
-          float* ta = reinterpret_cast<float*>(tab + c * 64 + (tq >> 1) * 16) + (tq & 1);
-          float* tb = reinterpret_cast<float*>(tab + (c + 4) * 64 + (tq >> 1) * 16) + (tq & 1);
-          ta[0] = d * sc_a; ta[2] = ndmin * mn_a;
-          tb[0] = d * sc_b; tb[2] = ndmin * mn_b;
+          // six-bit integers to fp32 through the 1.5 * 2^23 bias: stays off the conversion pipe
+          float const sc_a = __uint_as_float(kMagicI | (x0 & 63u)) - kMagicF, mn_a = __uint_as_float(kMagicI | (x1 & 63u)) - kMagicF;
+          float const sc_b = __uint_as_float(kMagicI | (x2 & 15u) | ((x0 >> 2) & 0x30u)) - kMagicF;
+          float const mn_b = __uint_as_float(kMagicI | ((x2 >> 4) & 15u) | ((x1 >> 2) & 0x30u)) - kMagicF;
+          tab_wa[0] = d * sc_a; tab_wa[2] = ndmin * mn_a;
+          tab_wb[0] = d * sc_b; tab_wb[2] = ndmin * mn_b;
         }
         uint32_t q[8];
         {
-          uint32_t const base = smem_u32(stage) + ldm_row * 128;
+          uint32_t const base = smem_u32(stage);
           uint32_t r4[4];
-          ldmatrix_x4(r4, base + ((ldm_mat ^ ldm_row) << 4));
+          ldmatrix_x4(r4, base + ldm_off0);
           q[0] = r4[0]; q[1] = r4[1]; q[2] = r4[2]; q[3] = r4[3];
-          ldmatrix_x4(r4, base + (((ldm_mat + 4) ^ ldm_row) << 4));
+          ldmatrix_x4(r4, base + ldm_off1);
           q[4] = r4[0]; q[5] = r4[1]; q[6] = r4[2]; q[7] = r4[3];
         }
         __syncwarp();
@@ -217,13 +279,16 @@ __global__ void __launch_bounds__(Warps * 32) gemv_mma_kernel(WeightView w, Q8Vi
           int d4[4];
           mma_s8(d4, lo.x, hi.x, lo.y, hi.y, b0, b1);
           float4 const f0 = *reinterpret_cast<const float4*>(f_ptr + g * (Tokens * 16));
-          float2 t = mul2(make_float2(dm.x, dm.y), make_float2(float(d4[0]), float(d4[1])));
-          t = fma2(make_float2(dm.z, dm.w), make_float2(f0.z, f0.w), t);
+          float2 const D2 = make_float2(dm.x, dm.y), nMn2 = make_float2(dm.z, dm.w);
+          float2 const cD2 = mul2(D2, nmagic2);  // exact: D has at most 17 significant bits
+          // D * float(P) in one rounding: (P + 1.5*2^23) * D - 1.5*2^23 * D
+          float2 t = fma2(make_float2(__uint_as_float(uint32_t(d4[0]) + kMagicI), __uint_as_float(uint32_t(d4[1]) + kMagicI)), D2, cD2);
+          t = fma2(nMn2, make_float2(f0.z, f0.w), t);
           acc_lo = fma2(make_float2(f0.x, f0.y), t, acc_lo);
           if (Upper) {
             float4 const f1 = *reinterpret_cast<const float4*>(f_ptr + g * (Tokens * 16) + 8 * 16);
-            float2 u = mul2(make_float2(dm.x, dm.y), make_float2(float(d4[2]), float(d4[3])));
-            u = fma2(make_float2(dm.z, dm.w), make_float2(f1.z, f1.w), u);
+            float2 u = fma2(make_float2(__uint_as_float(uint32_t(d4[2]) + kMagicI), __uint_as_float(uint32_t(d4[3]) + kMagicI)), D2, cD2);
+            u = fma2(nMn2, make_float2(f1.z, f1.w), u);
             acc_hi = fma2(make_float2(f1.x, f1.y), u, acc_hi);
           }
           if (Dump) {
@@ -235,13 +300,12 @@ __global__ void __launch_bounds__(Warps * 32) gemv_mma_kernel(WeightView w, Q8Vi
           }
         }
         __syncwarp();
-        if (next_load < kb1)
-          fill_stage<Wide>(ring + (next_load - kb0) % kStages * kStageBytes, cbase + uint64_t(next_load) * 1024,
-                           mbase + uint64_t(next_load) * 128, lane);
-        ++next_load;
-        cp_async_commit();
+        issue();
       }
     }
+    if (has_next) stage_store(cur ^ 1);
+    __syncthreads();
+    cur ^= 1;
   }
   cp_async_wait<0>();
 
