@@ -225,6 +225,11 @@ def main():
         if world > 1:
             dist.all_gather_into_tensor(gathered[(m, i)], outs[(m, i)])
 
+    def which_kernel(m, rows):
+        """The library's own dispatch rule for m <= 16 (csrc/abi.cu): dp4a for one or two tokens
+        and for up to four on matrices of >= 32768 rows, cluster MMA otherwise."""
+        return "dp4a" if (m <= 2 or (m <= 4 and rows >= 32768)) else "mma"
+
     def one_step(step, count=True, quantise=True, only_kernel=None):
         for mi, m in enumerate(TOKENS):
             layer = (step * len(TOKENS) + mi) % LAYERS
@@ -233,10 +238,9 @@ def main():
                     pack_q8(x_in[m][k], failure, out=q8[m][k])
                     if count:
                         launches["n"] += 1
-            kern = "dp4a" if m <= 4 else "mma"
-            if only_kernel and kern != only_kernel:
-                continue
             for i in range(len(SHAPES)):
+                if only_kernel and which_kernel(m, layers[layer][i].n) != only_kernel:
+                    continue
                 projection(m, i, layer, count)
 
     stream = torch.cuda.Stream(device=dev)
@@ -325,13 +329,13 @@ def main():
     # Per-kernel passes (all ranks take part so collectives match).
     per_kernel = {}
     for kern in ("dp4a", "mma"):
-        ms_list = [m for m in TOKENS if (m <= 4) == (kern == "dp4a")]
+        pairs = [(m, i) for m in TOKENS for i in range(len(SHAPES)) if which_kernel(m, layers[0][i].n) == kern]
         fn = (lambda s, kk=kern: one_step(s, count=False, quantise=False, only_kernel=kk))
         gk = capture(fn, UNROLL) if use_graph else Eager(fn, UNROLL)
         timed(gk, warm_replays)
         msk = timed(gk, replays)
-        n_launch = len(ms_list) * len(SHAPES) * steps
-        bytes_k = sum(algorithmic_bytes(m, n, k, with_quantise=False) for m in ms_list for _, n, k in SHAPES) * steps
+        n_launch = len(pairs) * steps
+        bytes_k = sum(algorithmic_bytes(m, SHAPES[i][1], SHAPES[i][2], with_quantise=False) for m, i in pairs) * steps
         per_kernel[kern] = {"launches": n_launch, "avg_us": msk * 1e3 / n_launch, "GBps": bytes_k / (msk * 1e-3) / 1e9,
                             "ms": msk, "bytes_per_launch": bytes_k / n_launch}
     per_m = {}
@@ -367,9 +371,10 @@ def main():
     e2e_value = total_bytes * steps / (ms_e2e * 1e-3) / 1e9
 
     prefill = None
+    peaks_all = json.loads((ROOT / "MEASURED_PEAKS.json").read_text()) if (ROOT / "MEASURED_PEAKS.json").exists() else {}
     if world == 1 and not args.no_prefill and not args.only:
         prefill = {}
-        for (m, n, k) in [(512, 17408, 5120), (512, 5120, 17408), (2048, 17408, 5120)]:
+        for (m, n, k) in [(512, 17408, 5120), (512, 5120, 17408), (2048, 17408, 5120), (8192, 17408, 5120)]:
             w = synth.device_weight(n, k, seed=99, device=dev)
             xq = pack_q8(torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16) * 0.5, failure)
             out = torch.empty((m, n), dtype=torch.float32, device=dev)
@@ -384,14 +389,18 @@ def main():
                 e1.record(stream)
             stream.synchronize()
             t = e0.elapsed_time(e1) / reps
-            prefill[f"M{m}_N{n}_K{k}"] = {"ms": round(t, 4), "int8_TOPS": round(2.0 * m * n * k / (t * 1e-3) / 1e12, 1)}
+            tops = 2.0 * m * n * k / (t * 1e-3) / 1e12
+            int8_peak = 2.0 * peaks_all.get("bf16_tflops", 1590.0)  # int8 dense nominal = 2x bf16; bf16 burst is measured
+            prefill[f"M{m}_N{n}_K{k}"] = {"ms": round(t, 4), "int8_TOPS": round(tops, 1), "kernel": "mmq_tcgen05_kernel",
+                                          "frac_of_2x_measured_bf16": round(tops / int8_peak, 4),
+                                          "frac_of_nominal_4500": round(tops / 4500.0, 4)}
             del w, out, xq
 
     if rank == 0:
         dom = max(per_kernel, key=lambda kk: per_kernel[kk]["ms"])
         pkk = per_kernel[dom]
         achieved = pkk["GBps"]
-        kernel_name = {"dp4a": "gemv_dp4a_kernel", "mma": "mmq_mma_kernel"}[dom]
+        kernel_name = {"dp4a": "gemv_dp4a_kernel", "mma": "gemv_mma_kernel"}[dom]
         line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm_replays * UNROLL,
                 "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8 dot / fp32 affine", "data": "synthetic",

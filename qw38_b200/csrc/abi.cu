@@ -188,11 +188,13 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
   if (int st = check_distinct(regions, count, trusted)) return st;
 
   uint32_t kernel = opt ? opt->kernel : Q4K_KERNEL_AUTO;
-  if (kernel == Q4K_KERNEL_AUTO)
-    kernel = x.m <= q4k::kGemvDp4aMaxTokens
-                 ? Q4K_KERNEL_GEMV_DP4A
-                 : (x.m <= 16 ? Q4K_KERNEL_GEMV_MMA
-                              : (q4k::tcgen05_supported(view(w), view(x)) ? Q4K_KERNEL_TCGEN05 : Q4K_KERNEL_MMA));
+  if (kernel == Q4K_KERNEL_AUTO) {
+    // dp4a for one or two tokens (and up to four on very tall matrices, where it measured
+    // faster), cluster MMA up to 16 tokens, tcgen05 beyond when TMA alignment allows.
+    if (x.m <= 2 || (x.m <= q4k::kGemvDp4aMaxTokens && w.padded_n >= 32768)) kernel = Q4K_KERNEL_GEMV_DP4A;
+    else if (x.m <= 16) kernel = Q4K_KERNEL_GEMV_MMA;
+    else kernel = q4k::tcgen05_supported(view(w), view(x)) ? Q4K_KERNEL_TCGEN05 : Q4K_KERNEL_MMA;
+  }
   const float* res = residual_len ? residual : nullptr;
   if (kernel == Q4K_KERNEL_GEMV_DP4A) {
     if (x.m > q4k::kGemvDp4aMaxTokens) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: dp4a kernel takes m <= 4");

@@ -373,13 +373,15 @@ GemvMmaPlan plan_gemv_mma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
   (void)m;
   GemvMmaPlan p;
   uint32_t const rgs = (n + 7) / 8;
-  // Row tiles of 4 row groups when 8 would leave too few blocks to balance 148 SMs.
-  p.warps = warps_request ? warps_request : ((rgs / 8) * 8 >= 148 * 16 ? 8 : 4);
+  // Eight row groups per block share one staged activation slice; measured best on every
+  // decode shape except very small matrices, where four keep more blocks in flight.
+  p.warps = warps_request ? warps_request : (rgs >= 8 * 64 ? 8 : 4);
   uint32_t const row_tiles = (rgs + p.warps - 1) / p.warps;
   uint32_t split = split_k_request;
   if (split == 0) {
-    // About ten blocks per SM balances the machine; a slice keeps at least four super-blocks.
-    split = (148 * 10 + row_tiles - 1) / row_tiles;
+    // About two blocks per SM; a slice keeps at least four super-blocks (measured optimum:
+    // 1 for 34816 rows, 2 for 7168, 4 for 5120 rows at K = 5120 / 17408).
+    split = uint32_t(296.0 / row_tiles + 0.35);
     uint32_t const max_split = tiles_k / 4 ? tiles_k / 4 : 1;
     if (split > max_split) split = max_split;
   }
