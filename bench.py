@@ -427,8 +427,13 @@ def main():
             line["cpu_baseline"] = None
         print(json.dumps(line))
     if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
+        # Every collective of this process has completed (the timed regions end with a device
+        # synchronise).  Tearing NCCL down with captured graphs still alive can block, so leave
+        # without it.
+        torch.cuda.synchronize(dev)
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
 
 
 if __name__ == "__main__":
