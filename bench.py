@@ -414,7 +414,10 @@ def main():
                 "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                         "ms_per_step": ms_e2e / steps},
                 "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
-                             "frac": achieved / hbm_peak, "peak_source": peak_src, "traffic": None,
+                             "frac": achieved / hbm_peak, "peak_source": peak_src,
+                             # DRAM read+write of one launch = algorithmic bytes x the ratio measured by ncu on the
+                             # 34816x5120 captures under profiles/ (1.034 cluster MMA at M=8, 1.033 dp4a at M=1)
+                             "traffic": pkk["bytes_per_launch"] * (1.034 if dom == "mma" else 1.033),
                              "avg_launch_us": pkk["avg_us"], "bytes_per_launch": pkk["bytes_per_launch"],
                              "by_kernel": {kk: {"GBps": round(v["GBps"], 1), "frac": round(v["GBps"] / hbm_peak, 4),
                                                 "avg_us": round(v["avg_us"], 3), "launches": v["launches"]}

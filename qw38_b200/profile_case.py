@@ -1,0 +1,19 @@
+"""Runs one projection a few times so that a profiler can capture a single kernel:
+    python -m qw38_b200.profile_case <n> <k> <m> <kernel id> [split_k] [row_groups]
+Kernel ids are the Q4K_KERNEL_* values of include/q4k_b200.h (1 dp4a, 2 mma, 3 tcgen05, 4 cluster mma)."""
+import sys, os
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import torch
+from qw38_b200 import synth
+from qw38_b200.q4k_q8 import pack_q8, q4k_q8_project
+n, k, m, kern = (int(a) for a in sys.argv[1:5])
+sk = int(sys.argv[5]) if len(sys.argv) > 5 else 0
+rg = int(sys.argv[6]) if len(sys.argv) > 6 else 0
+w = synth.device_weight(n, k, seed=0)
+f = torch.zeros(1, dtype=torch.int32, device="cuda")
+q = pack_q8(torch.randn((m, k), device="cuda").to(torch.bfloat16), f)
+out = torch.empty((m, n), dtype=torch.float32, device="cuda")
+for _ in range(3):
+    q4k_q8_project(w, q, out=out, kernel=kern, split_k=sk, row_groups=rg, trusted=True)
+torch.cuda.synchronize()
+print("ok", float(out.abs().mean()))
