@@ -71,11 +71,13 @@ typedef struct q4k_q8_input {
 #define Q4K_KERNEL_MMA 2       /* any m  : warp-level int8 mma, split-K through global scratch */
 #define Q4K_KERNEL_TCGEN05 3   /* m >= 32: tcgen05 kind::i8, TMEM accumulators */
 #define Q4K_KERNEL_GEMV_MMA 4  /* m <= 16: warp-level int8 mma, split-K inside a block cluster */
+#define Q4K_KERNEL_GEMV_TMA 5  /* m <= 16: weights streamed by TMA, activations held in registers */
 
 typedef struct q4k_project_options {
   uint32_t kernel;       /* Q4K_KERNEL_* */
   uint32_t split_k;      /* 0 = choose; otherwise number of K slices (mma kernels; <= 8 for GEMV_MMA) */
-  uint32_t row_groups;   /* 0 = choose; row groups (of 8 rows) per block, 4 or 8 (GEMV_MMA) */
+  uint32_t row_groups;   /* 0 = choose; row groups (of 8 rows) per block, 4 or 8 (GEMV_MMA);
+                          * super-blocks per K slice, <= 20 (GEMV_TMA) */
   int32_t* partials;     /* optional: int32 dots [m][n][padded_k/32], bit-exact check */
   uint64_t partials_len; /* element count of partials, m*n*padded_k/32 when given */
   void* workspace;       /* optional scratch for split-K; NULL = library-owned scratch */

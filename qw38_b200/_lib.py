@@ -11,7 +11,7 @@ from . import build as _build
 
 OK, ERR_STATUS, ERR_INVALID_ARGUMENT, ERR_OVERFLOW = 0, 1, 2, 3
 LAYOUT_SPLIT_TILES, QUANTIZER_Q4K = 0x020D, 0x0105
-KERNEL_AUTO, KERNEL_GEMV_DP4A, KERNEL_MMA, KERNEL_TCGEN05, KERNEL_GEMV_MMA = 0, 1, 2, 3, 4
+KERNEL_AUTO, KERNEL_GEMV_DP4A, KERNEL_MMA, KERNEL_TCGEN05, KERNEL_GEMV_MMA, KERNEL_GEMV_TMA = 0, 1, 2, 3, 4, 5
 FLAG_TRUSTED_SPANS = 1
 
 

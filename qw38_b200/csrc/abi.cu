@@ -210,6 +210,27 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
     Q4K_CUDA(q4k::launch_gemv_mma(view(w), view(x), output, res, partials, plan, stream), "q4k_q8.gemv_mma");
     return Q4K_OK;
   }
+  if (kernel == Q4K_KERNEL_GEMV_TMA) {
+    if (!q4k::gemv_tma_supported(view(w), view(x)))
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: the TMA gemv kernel takes m <= 16 and 16-byte aligned weights");
+    q4k::GemvTmaPlan plan = q4k::plan_gemv_tma(x.m, w.n, w.padded_k / 256, opt ? opt->split_k : 0, opt ? opt->row_groups : 0);
+    uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
+    void* scratch = nullptr;
+    if (opt && opt->workspace) {
+      if (opt->workspace_bytes < kTicketRegion + partial_bytes)
+        return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: workspace too small");
+      scratch = opt->workspace;
+      Q4K_CUDA(cudaMemsetAsync(scratch, 0, kTicketRegion, stream), "q4k_q8.clear_tickets");
+    } else if (int st = own_scratch(partial_bytes, &scratch)) {
+      return st;
+    }
+    int* status = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch) + kTicketRegion - 4);
+    Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), output, res, partials, plan,
+                                  static_cast<uint8_t*>(scratch) + kTicketRegion, static_cast<uint32_t*>(scratch),
+                                  status, stream),
+             "q4k_q8.gemv_tma");
+    return Q4K_OK;
+  }
   if (kernel == Q4K_KERNEL_TCGEN05) {
     if (!q4k::tcgen05_supported(view(w), view(x)))
       return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: the tcgen05 kernel needs 16-byte aligned operands");

@@ -1,0 +1,478 @@
+// Decode projection (m <= 16) with the activations held in registers and the weights streamed
+// through shared memory by TMA.
+//
+// The 4-bit weights are read exactly once and are the only large operand, so the kernel is
+// built around keeping many weight bytes in flight per SM with no instruction cost: one
+// producer lane issues two bulk tensor copies per stage (code tiles with the 128-byte swizzle,
+// metadata tiles) into a ring that holds most of shared memory.  The work is laid out
+// "K-stationary": consumer warp w owns super-block column sb0 + w of the block's K slice for
+// the whole kernel and keeps everything that depends on (token, K) in registers -- the int8
+// activation fragments of its eight K32 groups, the activation scales, and a * sum split into
+// three tf32 terms -- while the block walks down its range of 16-row tiles.  Per tile a consumer
+//   * decodes the 16 rows' six-bit scales/mins of its super-block into a small float table,
+//   * ldmatrix's the swizzled code tile into mma A fragments (nibbles -> u8 by mask/shift),
+//   * issues one m16n8k32 u8*s8 MMA per K32 group and token octet whose accumulator input is the
+//     bit pattern of 1.5*2^23, so the int32 result *is* the float 1.5*2^23 + dot (exact, |dot| <
+//     2^22) and no int->float conversion is issued,
+//   * folds  a * (sc * dot)  with two packed fp32 FMAs per pair of partials, and the min term
+//     sum_g mn[row,g] * (a*sum)[tok,g] with three m16n8k8 tf32 MMAs (mn is a 6-bit integer and the
+//     three tf32 terms add up to the fp32 value exactly, so the products are exact),
+//   * scales by d / dmin and hands its 16 x m partial tile to the reducer warp, which adds the
+//     consumers' tiles in warp order and writes the rows (or the K slice's scratch tile).
+// K slices of different blocks are added in slice order by the last block to finish a row range
+// (arrival ticket), as in the other split-K kernels of this library.
+//
+// Contract notes (reference: cuda/q4k_q8.cu:63-112, mmvq): the int32 dot of a K32 group is exact
+// and never carried into the next group; scales stay fp32.  Every mbarrier wait is bounded.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "launch.h"
+#include "tma.cuh"
+
+namespace q4k {
+namespace {
+
+constexpr uint32_t kMagicI = 0x4B400000u;  // bit pattern of 1.5 * 2^23
+constexpr float kMagicF = 12582912.0f;
+constexpr int kProducer = 0, kReducer = 1, kFirstConsumer = 2;
+// per consumer warp: 1280 scale pairs (16 rows, stride 80 bytes so that the eight rows a load touches fall in
+// different banks), 768 mins (row stride 12 floats), 256 d/dmin, then NT * 256 activation scale pairs
+constexpr int kTabBytes = 2304, kTabMn = 1280, kTabDd = 2048;
+constexpr int kMaxStages = 8;
+
+struct GtParams {
+  const int8_t* xcodes;
+  const float* xscales;
+  const int32_t* xsums;
+  const float* residual;
+  float* out;
+  int32_t* partials;  // optional int32 K32 dots [m][n][G]
+  float* slices;      // split-K scratch [slice][m][n]
+  uint32_t* tickets;  // one per row range, zero on entry and on exit
+  int* status;
+  uint32_t n, m, padded_k, tiles_k, G;
+  uint32_t row_tiles;        // 16-row tiles
+  uint32_t cw;               // consumer warps = super-blocks per K slice
+  uint32_t split_k, tiles_per_range, stages;
+  uint32_t red_slots;        // 1 or 2 hand-off buffers between the consumers and the reducer
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+// D = A(u8, 16x32) * B(s8, 32x8) + C.  C is a block of four registers that the caller fills once
+// and keeps alive, so that no per-MMA moves are needed to build the accumulator input.
+__device__ __forceinline__ void mma_u8s8(uint32_t (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                         uint32_t b0, uint32_t b1, const uint32_t (&c)[4]) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%11,%12,%13};\n"
+      : "=r"(d[0]), "=r"(d[1]), "=r"(d[2]), "=r"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(c[0]), "r"(c[1]), "r"(c[2]), "r"(c[3]));
+}
+__device__ __forceinline__ void mma_tf32(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k8.row.col.f32.tf32.tf32.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t to_tf32(float v) {
+  uint32_t r;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
+  return r;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __ffma2_rn(a, b, c); }
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
+__device__ __forceinline__ float2 as_f2(uint32_t x, uint32_t y) { return make_float2(__uint_as_float(x), __uint_as_float(y)); }
+
+// Shared-memory accesses by 32-bit shared-space address (generic pointers into the dynamic
+// buffer would cost 64-bit address arithmetic and generic loads on every access).
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts128f(uint32_t a, float x, float y, float z, float w) {
+  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+
+// NT = token octets (1: m <= 8, 2: m <= 16).  MAXW bounds the block size for register allocation.
+template <int NT, int MAXW, bool Dump>
+__global__ void __launch_bounds__(MAXW * 32, 1)
+gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_constant__ CUtensorMap tm_meta, const GtParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint32_t const smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint32_t const cw = p.cw, stages = p.stages;
+  uint32_t const code_stage = cw * 2048, meta_stage = cw * 256;
+  uint32_t const s_codes = smem;
+  uint32_t const s_meta = s_codes + stages * code_stage;
+  uint32_t const s_tab = s_meta + stages * meta_stage;
+  uint32_t const tab_bytes = kTabBytes + NT * 256;
+  uint32_t const s_red = s_tab + cw * tab_bytes;
+  uint32_t const red_slot = cw * NT * 512;
+  // barriers: full[stages] empty[stages] red_full[2] red_empty[2], then the abort and "last block" flags
+  uint32_t const b_full = s_red + p.red_slots * red_slot, b_empty = b_full + 8 * stages, b_rfull = b_empty + 8 * stages, b_rempty = b_rfull + 16;
+  int* const flags = reinterpret_cast<int*>(smem_raw + (b_rempty + 16 - smem_u32(smem_raw)));
+  volatile int* const abort_flag = flags;
+  int* const last_flag = flags + 1;
+
+  uint32_t const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  bool const two_slots = p.red_slots == 2;
+  uint32_t const range = blockIdx.x / p.split_k, slice = blockIdx.x % p.split_k;
+  uint32_t const sb0 = slice * cw;
+  uint32_t const nact = min(cw, p.tiles_k - sb0);  // consumer warps with a real super-block
+  uint32_t const t0 = range * p.tiles_per_range;
+  uint32_t const t1 = min(p.row_tiles, t0 + p.tiles_per_range);
+  uint32_t const ntiles = t1 > t0 ? t1 - t0 : 0;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t s = 0; s < stages; ++s) {
+      mbar_init(b_full + 8 * s, 1);
+      mbar_init(b_empty + 8 * s, nact * 32);
+    }
+    for (uint32_t s = 0; s < 2; ++s) {
+      mbar_init(b_rfull + 8 * s, nact * 32);
+      mbar_init(b_rempty + 8 * s, 32);
+    }
+    *abort_flag = 0;
+    *last_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+
+  if (warp == kProducer) {
+    if (lane == 0) {
+      uint32_t s = 0, ph = 1;  // the first pass over the ring finds every stage free
+      for (uint32_t it = 0; it < ntiles; ++it) {
+        if (it >= stages && !mbar_wait(b_empty + 8 * s, ph, abort_flag, p.status, 0x510)) break;
+        mbar_expect_tx(b_full + 8 * s, code_stage + meta_stage);
+        int const rg = int((t0 + it) * 2);
+        tma_3d(s_codes + s * code_stage, &tm_codes, 0, int(sb0 * 8), rg, b_full + 8 * s);
+        tma_3d(s_meta + s * meta_stage, &tm_meta, 0, int(sb0), rg, b_full + 8 * s);
+        if (++s == stages) { s = 0; ph ^= 1; }
+      }
+    }
+  } else if (warp == kReducer) {
+    // Adds the consumers' 16 x (8*NT) tiles in warp order.  Lane (r = lane/4, q = lane%4) owns
+    // rows r, r+8 and tokens 2q, 2q+1 of every octet -- the MMA accumulator layout.
+    uint32_t const r = lane >> 2, q = lane & 3;
+    float* const dst = p.split_k > 1 ? p.slices + size_t(slice) * p.m * p.n : p.out;
+    bool const add_residual = p.split_k == 1 && p.residual != nullptr;
+    for (uint32_t it = 0; it < ntiles; ++it) {
+      uint32_t const s = two_slots ? it & 1 : 0, use = two_slots ? it >> 1 : it;
+      if (!mbar_wait(b_rfull + 8 * s, use & 1, abort_flag, p.status, 0x520)) break;
+      float4 acc[NT];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) acc[nt] = make_float4(0.f, 0.f, 0.f, 0.f);
+      uint32_t src = s_red + s * red_slot + lane * 16;
+      for (uint32_t w = 0; w < nact; ++w) {
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          float4 const v = lds128f(src + nt * 512);
+          acc[nt].x += v.x; acc[nt].y += v.y; acc[nt].z += v.z; acc[nt].w += v.w;
+        }
+        src += NT * 512;
+      }
+      mbar_arrive(b_rempty + 8 * s);
+      uint32_t const row = (t0 + it) * 16 + r;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float const v[4] = {acc[nt].x, acc[nt].y, acc[nt].z, acc[nt].w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint32_t const tok = nt * 8 + q * 2 + (j & 1), rr = row + (j >> 1) * 8;
+          if (tok < p.m && rr < p.n) {
+            size_t const o = size_t(tok) * p.n + rr;
+            float val = v[j];
+            if (add_residual) val += p.residual[o];
+            dst[o] = val;
+          }
+        }
+      }
+    }
+    __threadfence();
+  } else if (warp - kFirstConsumer < nact) {
+    uint32_t const w = warp - kFirstConsumer, sb = sb0 + w;
+    uint32_t const r = lane >> 2, q = lane & 3;
+    // ---- K-stationary operands ----
+    uint32_t const tab = s_tab + w * tab_bytes;
+    // activation scale pairs {a[2q], a[2q+1]} of (octet nt, group g) at ((nt*4 + g/2)*4 + q)*16 + (g%2)*8
+    uint32_t const rd_ap = tab + kTabBytes + q * 16;
+    uint32_t bfrag[NT][8][2];  // int8 activations of token nt*8 + r: even / odd columns of 8q..8q+7 in group g
+    uint32_t asplit[NT][3][2]; // tf32 terms of a*sum for token nt*8 + r, groups q and q+4
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      uint32_t const tokb = nt * 8 + r, tokc = nt * 8 + 2 * q;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        uint2 z = make_uint2(0u, 0u);
+        if (tokb < p.m) z = *reinterpret_cast<const uint2*>(p.xcodes + size_t(tokb) * p.padded_k + sb * 256 + g * 32 + q * 8);
+        bfrag[nt][g][0] = even_bytes(z.x, z.y);
+        bfrag[nt][g][1] = odd_bytes(z.x, z.y);
+        if (r == 0) {  // lanes 0..3 fill the scale-pair table of this warp
+          float const a0 = tokc < p.m ? p.xscales[size_t(tokc) * p.G + sb * 8 + g] : 0.f;
+          float const a1 = tokc + 1 < p.m ? p.xscales[size_t(tokc + 1) * p.G + sb * 8 + g] : 0.f;
+          asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(rd_ap + (nt * 4 + g / 2) * 64 + (g % 2) * 8), "f"(a0), "f"(a1) : "memory");
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float as = 0.f;
+        if (tokb < p.m) {
+          size_t const i = size_t(tokb) * p.G + sb * 8 + q + 4 * h;
+          as = p.xscales[i] * float(p.xsums[i]);
+        }
+        uint32_t const hi = to_tf32(as);
+        float const r1 = as - __uint_as_float(hi);
+        uint32_t const mid = to_tf32(r1);
+        float const r2 = r1 - __uint_as_float(mid);
+        asplit[nt][0][h] = hi;
+        asplit[nt][1][h] = mid;
+        asplit[nt][2][h] = to_tf32(r2);
+      }
+    }
+    __syncwarp();
+    float2 const nmagic2 = make_float2(-kMagicF, -kMagicF);
+    uint32_t cmagic[4];  // accumulator input of every MMA; opaque to the compiler so that it stays in four registers
+#pragma unroll
+    for (int j = 0; j < 4; ++j) asm volatile("mov.u32 %0, %1;" : "=r"(cmagic[j]) : "n"(0x4B400000));
+    // decode role of this lane: row16 = lane & 15, half h = lane >> 4 takes groups 4h..4h+3
+    uint32_t const drow = lane & 15, dh = lane >> 4;
+    // groups 0..3: byte & 0x3f; groups 4..7: (byte of word 3 & 0x0f) | ((byte >> 2) & 0x30)  (mins: high nibble of word 3)
+    uint32_t const dsh = dh ? 2u : 0u, dmask_a = dh ? 0x30303030u : 0x3f3f3f3fu, dmask_b = dh ? 0x0f0f0f0fu : 0u;
+    uint32_t const dec_meta = s_meta + (drow >> 3) * cw * 128 + w * 128 + (drow & 7) * 16;
+    uint32_t const dec_sc = tab + drow * 80 + dh * 32, dec_mn = tab + kTabMn + drow * 48 + dh * 16, dec_dd = tab + kTabDd + drow * 16;
+    uint32_t const rd_sc = tab + r * 80, rd_mn = tab + kTabMn + r * 48 + q * 4, rd_dd = tab + kTabDd + r * 16;
+    // ldmatrix lane address: matrix j = lane >> 3 (bit 0: row group, bit 1: second K32 group), row i = lane & 7
+    uint32_t const lj = lane >> 3, li = lane & 7;
+    uint32_t const ld_base = s_codes + (lj & 1) * cw * 1024 + w * 1024 + li * 128;
+    uint32_t const ld_x = ((lj >> 1) << 4) ^ (li << 4);
+    uint32_t const red_dst = s_red + (w * NT * 32 + lane) * 16;
+
+    uint32_t s = 0, ph = 0, code_off = 0, meta_off = 0;
+    for (uint32_t it = 0; it < ntiles; ++it) {
+      if (!mbar_wait(b_full + 8 * s, ph, abort_flag, p.status, 0x530)) break;
+      // ---- decode the metadata of 16 rows ----
+      {
+        uint4 const mw = lds128(dec_meta + meta_off);
+        uint32_t const sc4 = ((mw.y >> dsh) & dmask_a) | (mw.w & dmask_b);
+        uint32_t const mn4 = ((mw.z >> dsh) & dmask_a) | ((mw.w >> 4) & dmask_b);
+        float const s0 = float(sc4 & 0xffu), s1 = float((sc4 >> 8) & 0xffu), s2 = float((sc4 >> 16) & 0xffu), s3 = float(sc4 >> 24);
+        sts128f(dec_sc, s0, s0, s1, s1);
+        sts128f(dec_sc + 16, s2, s2, s3, s3);
+        sts128f(dec_mn, float(mn4 & 0xffu), float((mn4 >> 8) & 0xffu), float((mn4 >> 16) & 0xffu), float(mn4 >> 24));
+        float const d = fp16_bits_to_f32(mw.x & 0xffffu), ndmin = -fp16_bits_to_f32(mw.x >> 16);
+        sts128f(dec_dd, d, d, ndmin, ndmin);  // both halves of a row store the same words
+      }
+      __syncwarp();
+      float2 acc[NT][2];
+      float mins[NT][4];
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        acc[nt][0] = acc[nt][1] = make_float2(0.f, 0.f);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) mins[nt][j] = 0.f;
+      }
+      uint32_t const cbase = ld_base + code_off;
+#pragma unroll
+      for (int gp = 0; gp < 4; ++gp) {
+        uint32_t raw[4];
+        ldmatrix_x4(raw, cbase + ((uint32_t(gp) << 5) ^ ld_x));
+        float4 const sc_lo = lds128f(rd_sc + gp * 16);         // row r:   {s_g, s_g, s_g+1, s_g+1}
+        float4 const sc_hi = lds128f(rd_sc + 640 + gp * 16);   // row r+8
+        float4 ap4[NT];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) ap4[nt] = lds128f(rd_ap + (nt * 4 + gp) * 64);
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          int const g = gp * 2 + e;
+          uint32_t const w0 = raw[2 * e], w1 = raw[2 * e + 1];
+          uint32_t const a0 = w0 & 0x0f0f0f0fu, a1 = w1 & 0x0f0f0f0fu;
+          uint32_t const a2 = (w0 >> 4) & 0x0f0f0f0fu, a3 = (w1 >> 4) & 0x0f0f0f0fu;
+          float2 const s_lo = e ? make_float2(sc_lo.z, sc_lo.w) : make_float2(sc_lo.x, sc_lo.y);
+          float2 const s_hi = e ? make_float2(sc_hi.z, sc_hi.w) : make_float2(sc_hi.x, sc_hi.y);
+          float2 const c_lo = mul2(s_lo, nmagic2), c_hi = mul2(s_hi, nmagic2);  // exact: 6-bit integer * 1.5*2^23
+#pragma unroll
+          for (int nt = 0; nt < NT; ++nt) {
+            uint32_t d[4];
+            mma_u8s8(d, a0, a1, a2, a3, bfrag[nt][g][0], bfrag[nt][g][1], cmagic);
+            if constexpr (Dump) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                uint32_t const tok = nt * 8 + q * 2 + (j & 1), row = (t0 + it) * 16 + r + (j >> 1) * 8;
+                if (tok < p.m && row < p.n) p.partials[(size_t(tok) * p.n + row) * p.G + sb * 8 + g] = int32_t(d[j] - kMagicI);
+              }
+            }
+            float2 const ap = e ? make_float2(ap4[nt].z, ap4[nt].w) : make_float2(ap4[nt].x, ap4[nt].y);
+            float2 const t_lo = fma2(as_f2(d[0], d[1]), s_lo, c_lo);  // sc * dot, exact
+            float2 const t_hi = fma2(as_f2(d[2], d[3]), s_hi, c_hi);
+            acc[nt][0] = fma2(t_lo, ap, acc[nt][0]);
+            acc[nt][1] = fma2(t_hi, ap, acc[nt][1]);
+          }
+        }
+      }
+      // ---- min term: rows x groups (6-bit integers) times groups x tokens (three tf32 terms of a*sum) ----
+      {
+        uint32_t const m0 = lds32(rd_mn), m1 = lds32(rd_mn + 384), m2 = lds32(rd_mn + 16), m3 = lds32(rd_mn + 400);
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+#pragma unroll
+          for (int part = 2; part >= 0; --part) mma_tf32(mins[nt], m0, m1, m2, m3, asplit[nt][part][0], asplit[nt][part][1]);
+        }
+      }
+      float4 const dd_lo = lds128f(rd_dd);        // {d, d, -dmin, -dmin} of row r
+      float4 const dd_hi = lds128f(rd_dd + 128);  // row r+8
+      mbar_arrive(b_empty + 8 * s);  // this lane has consumed its part of the stage's code and metadata tiles
+      // ---- hand the tile to the reducer ----
+      uint32_t const rs = two_slots ? it & 1 : 0, ruse = two_slots ? it >> 1 : it;
+      if (ruse > 0 && !mbar_wait(b_rempty + 8 * rs, (ruse - 1) & 1, abort_flag, p.status, 0x540)) break;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        float2 const o_lo = fma2(acc[nt][0], make_float2(dd_lo.x, dd_lo.y),
+                                 mul2(make_float2(mins[nt][0], mins[nt][1]), make_float2(dd_lo.z, dd_lo.w)));
+        float2 const o_hi = fma2(acc[nt][1], make_float2(dd_hi.x, dd_hi.y),
+                                 mul2(make_float2(mins[nt][2], mins[nt][3]), make_float2(dd_hi.z, dd_hi.w)));
+        sts128f(red_dst + rs * red_slot + nt * 512, o_lo.x, o_lo.y, o_hi.x, o_hi.y);
+      }
+      mbar_arrive(b_rfull + 8 * rs);
+      __syncwarp();  // every lane has read the tables before the next tile's decode overwrites them
+      code_off += code_stage;
+      meta_off += meta_stage;
+      if (++s == stages) { s = 0; ph ^= 1; code_off = 0; meta_off = 0; }
+    }
+  }
+
+  // ---- split-K: the last block of a row range adds the slices in order ----
+  if (p.split_k > 1) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      uint32_t const old = atomicAdd(p.tickets + range, 1u);
+      *last_flag = (old == p.split_k - 1) && !*abort_flag;
+      if (old == p.split_k - 1) p.tickets[range] = 0;
+    }
+    __syncthreads();
+    if (*last_flag) {
+      __threadfence();
+      uint32_t const row0 = t0 * 16, rows = min(p.n, t1 * 16) > row0 ? min(p.n, t1 * 16) - row0 : 0;
+      for (uint32_t i = threadIdx.x; i < rows * p.m; i += blockDim.x) {
+        uint32_t const tok = i / rows, row = row0 + i % rows;
+        size_t const o = size_t(tok) * p.n + row;
+        float v = __ldcg(p.slices + o);
+        for (uint32_t sl = 1; sl < p.split_k; ++sl) v += __ldcg(p.slices + size_t(sl) * p.m * p.n + o);
+        if (p.residual) v += p.residual[o];
+        p.out[o] = v;
+      }
+    }
+  }
+}
+
+}  // namespace
+
+namespace {
+
+constexpr uint32_t kSmemBudget = 227 * 1024;
+
+uint32_t smem_bytes(uint32_t cw, uint32_t nt, uint32_t stages, uint32_t red_slots) {
+  return 1024 + stages * cw * 2304 + cw * (kTabBytes + nt * 256) + red_slots * cw * nt * 512 + (2 * stages + 4) * 8 + 16;
+}
+
+template <int NT, int MAXW>
+cudaError_t launch_cfg(const CUtensorMap& tm_codes, const CUtensorMap& tm_meta, const GtParams& p, bool dump, uint32_t grid,
+                       uint32_t smem, cudaStream_t stream) {
+  auto kernel = dump ? gemv_tma_kernel<NT, MAXW, true> : gemv_tma_kernel<NT, MAXW, false>;
+  cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+  if (st != cudaSuccess) return st;
+  kernel<<<grid, (p.cw + kFirstConsumer) * 32, smem, stream>>>(tm_codes, tm_meta, p);
+  return cudaGetLastError();
+}
+
+}  // namespace
+
+bool gemv_tma_supported(const WeightView& w, const Q8View& x) {
+  return x.m <= kGemvTmaMaxTokens && encode_fn() != nullptr && reinterpret_cast<uintptr_t>(w.codes) % 16 == 0 &&
+         reinterpret_cast<uintptr_t>(w.meta) % 16 == 0 && reinterpret_cast<uintptr_t>(x.codes) % 8 == 0;
+}
+
+GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request, uint32_t warps_request) {
+  GemvTmaPlan p;
+  uint32_t const nt = m <= 8 ? 1 : 2;
+  uint32_t const max_cw = nt == 1 ? kGemvTmaMaxWarpsNarrow : kGemvTmaMaxWarpsWide;
+  uint32_t split = split_k_request;
+  if (split == 0) {
+    uint32_t const cw_target = warps_request ? (warps_request < max_cw ? warps_request : max_cw) : max_cw;
+    split = (tiles_k + cw_target - 1) / cw_target;
+  }
+  if (split > tiles_k) split = tiles_k;
+  if (split < 1) split = 1;
+  uint32_t cw = (tiles_k + split - 1) / split;
+  while (cw > max_cw) { ++split; cw = (tiles_k + split - 1) / split; }
+  split = (tiles_k + cw - 1) / cw;  // drop empty slices
+  p.split_k = split;
+  p.warps = cw;
+  uint32_t const row_tiles = ((n + 7) / 8 * 8 + 15) / 16;
+  uint32_t ranges = uint32_t(sm_count()) / split;
+  if (ranges < 1) ranges = 1;
+  if (ranges > row_tiles) ranges = row_tiles;
+  p.tiles_per_range = (row_tiles + ranges - 1) / ranges;
+  p.ranges = (row_tiles + p.tiles_per_range - 1) / p.tiles_per_range;
+  // Two hand-off buffers unless giving one up buys a third (or second) ring stage.
+  auto fit = [&](uint32_t slots) {
+    uint32_t st = 1;
+    while (st < uint32_t(kMaxStages) && smem_bytes(cw, nt, st + 1, slots) <= kSmemBudget) ++st;
+    return st;
+  };
+  p.red_slots = 2;
+  p.stages = fit(2);
+  if (p.stages < 3 && fit(1) > p.stages) { p.red_slots = 1; p.stages = fit(1); }
+  return p;
+}
+
+cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
+                            const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream) {
+  uint32_t const nt = x.m <= 8 ? 1 : 2;
+  uint32_t const cw = plan.warps;
+  if (x.m == 0 || x.m > kGemvTmaMaxTokens || cw < 1 || cw > (nt == 1 ? kGemvTmaMaxWarpsNarrow : kGemvTmaMaxWarpsWide) ||
+      plan.split_k * cw < w.tiles_k || plan.stages < 2 || plan.stages > uint32_t(kMaxStages) ||
+      (plan.red_slots != 1 && plan.red_slots != 2) || smem_bytes(cw, nt, plan.stages, plan.red_slots) > kSmemBudget || (plan.split_k > 1 && (!slices || !tickets)))
+    return cudaErrorInvalidValue;
+  CUtensorMap tm_codes, tm_meta;
+  uint64_t const rgs = w.padded_n / 8;
+  {
+    uint64_t dims[3] = {128, uint64_t(w.tiles_k) * 8, rgs}, strides[2] = {128, uint64_t(w.tiles_k) * 1024};
+    uint32_t box[3] = {128, cw * 8, 2};
+    if (!make_map(&tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
+      return cudaErrorInvalidValue;
+  }
+  {
+    uint64_t dims[3] = {128, w.tiles_k, rgs}, strides[2] = {128, uint64_t(w.tiles_k) * 128};
+    uint32_t box[3] = {128, cw, 2};
+    if (!make_map(&tm_meta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.meta, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return cudaErrorInvalidValue;
+  }
+  GtParams p{x.codes, x.scales, x.sums, residual, out, partials, static_cast<float*>(slices), tickets, status,
+             w.n, x.m, x.padded_k, w.tiles_k, x.padded_k / 32, (w.padded_n + 15) / 16, cw, plan.split_k,
+             plan.tiles_per_range, plan.stages, plan.red_slots};
+  uint32_t const grid = plan.ranges * plan.split_k, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
+  bool const dump = partials != nullptr;
+  if (nt == 1) {
+    if (cw <= 12) return launch_cfg<1, 14>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+    return launch_cfg<1, kGemvTmaMaxWarpsNarrow + 2>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+  }
+  if (cw <= 12) return launch_cfg<2, 14>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+  return launch_cfg<2, kGemvTmaMaxWarpsWide + 2>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+}
+
+}  // namespace q4k

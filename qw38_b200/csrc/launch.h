@@ -66,6 +66,25 @@ cudaError_t launch_mmq_tcgen05(const WeightView& w, const Q8View& x, float* out,
                                int32_t* partials, const TcPlan& plan, void* partial_tiles, uint32_t* tickets,
                                int* status, cudaStream_t stream);
 
+// gemv_tma.cu : m <= 16.  Weights streamed by TMA into a shared-memory ring, activations held in
+// registers by warps that each own one super-block column of the block's K slice; K slices of
+// different blocks are added in slice order through `slices` ([split_k][m][n] floats) by the last
+// block of a row range (`tickets`: one zeroed uint32 per range, left zero).
+constexpr uint32_t kGemvTmaMaxTokens = 16;
+constexpr uint32_t kGemvTmaMaxWarpsNarrow = 20;  // m <= 8
+constexpr uint32_t kGemvTmaMaxWarpsWide = 20;    // m <= 16
+struct GemvTmaPlan {
+  uint32_t warps;    // consumer warps = super-blocks per K slice
+  uint32_t split_k;  // K slices
+  uint32_t ranges, tiles_per_range;  // row ranges (blocks per slice) and 16-row tiles per range
+  uint32_t stages;   // depth of the weight ring
+  uint32_t red_slots;  // hand-off buffers between consumers and reducer: 1 or 2
+};
+bool gemv_tma_supported(const WeightView& w, const Q8View& x);
+GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request, uint32_t warps_request);
+cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
+                            const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream);
+
 // abi.cu : records the thread-local error text behind q4k_last_error() and returns `code`.
 int set_error(int code, const char* fmt, ...);
 int set_error_cuda(cudaError_t status, const char* operation);

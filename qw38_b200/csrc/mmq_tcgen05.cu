@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "launch.h"
+#include "tma.cuh"
 
 namespace q4k {
 namespace {
@@ -38,7 +39,6 @@ constexpr int kRows = 128;
 constexpr int kProducerWarp = 0, kMmaWarp = 1, kFirstExpander = 2;
 constexpr uint32_t kMagicI = 0x4B400000u;   // bit pattern of 1.5 * 2^23
 constexpr float kMagicF = 12582912.0f;
-constexpr long long kWaitCycles = 4000000000LL;
 
 // NTOK tokens per tile; NCOL <= NTOK accumulator columns actually drained (8 when m <= 8).
 //
@@ -99,51 +99,6 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kSmem = oCtrl + kBarriers * 8 + 64 + 1024 /*alignment slack*/;
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
 };
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-// Bounded wait for the phase with the given parity.  False = gave up (abort raised).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
-  {  // fast path: already complete
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-  }
-  long long const t0 = clock64();
-  for (uint32_t spin = 0;; ++spin) {
-    uint32_t ok;
-    asm volatile("{ .reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
-                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
-    if (ok) return true;
-    if ((spin & 15u) == 15u) {
-      if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitCycles) {
-        *abort_flag = 1;
-        atomicExch(status, code);
-        return false;
-      }
-    }
-  }
-}
-
-__device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
-  asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-               ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
-}
 
 // K-major, 128-byte swizzle: 8-row atoms of 1024 bytes; version 1; layout type 2.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
@@ -581,45 +536,6 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
 }
 
 // ------------------------------------------------------------------------------------------
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-EncodeTiled encode_fn() {
-  static EncodeTiled fn = [] {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      ptr = nullptr;
-    (void)cudaGetLastError();
-    return reinterpret_cast<EncodeTiled>(ptr);
-  }();
-  return fn;
-}
-
-bool make_map(CUtensorMap* map, CUtensorMapDataType type, uint32_t rank, const void* base, const uint64_t* dims,
-              const uint64_t* strides_bytes, const uint32_t* box, CUtensorMapSwizzle swizzle) {
-  EncodeTiled fn = encode_fn();
-  if (!fn) return false;
-  cuuint64_t d[3], st[2];
-  cuuint32_t b[3], es[3] = {1, 1, 1};
-  for (uint32_t i = 0; i < rank; ++i) { d[i] = dims[i]; b[i] = box[i]; }
-  for (uint32_t i = 0; i + 1 < rank; ++i) st[i] = strides_bytes[i];
-  return fn(map, type, rank, const_cast<void*>(base), d, st, b, es, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
-}
-
-int sm_count() {
-  static int count = [] {
-    int dev = 0, n = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
-      n = 148;
-    (void)cudaGetLastError();
-    return n;
-  }();
-  return count;
-}
-
 template <int NTOK, int NCOL>
 cudaError_t launch_ntok(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
                         uint32_t split_k, float* partial_tiles, uint32_t* tickets, int* status, cudaStream_t stream) {

@@ -44,7 +44,7 @@ def fixture_a(golden):
 
 
 def kernels_for(m):
-    return (([L.KERNEL_GEMV_DP4A] if m <= 4 else []) + ([L.KERNEL_GEMV_MMA] if m <= 16 else []) +
+    return (([L.KERNEL_GEMV_DP4A] if m <= 4 else []) + ([L.KERNEL_GEMV_MMA, L.KERNEL_GEMV_TMA] if m <= 16 else []) +
             [L.KERNEL_MMA, L.KERNEL_TCGEN05])
 
 
@@ -93,9 +93,11 @@ def test_reference_case(fixture_a, m):
         shifted_z = torch.full((pk + 8,), 99, dtype=torch.int8, device=DEV)
         shifted_z[4:-4] = q.codes[0]
         residual = dev(((np.arange(n) % 17) - 8).astype(np.float32) * 0.125)
-        with pytest.raises(Q4KError):   # TMA needs 16-byte aligned operands: a clear rejection, not a fault
-            q4k_q8_project(PrefillWeight(shifted_w[4:-4], w.scales, n, k), q, kernel=L.KERNEL_TCGEN05)
-        for kern in [kk for kk in kernels_for(1) if kk != L.KERNEL_TCGEN05]:
+        tma_kernels = (L.KERNEL_TCGEN05, L.KERNEL_GEMV_TMA)
+        for kern in tma_kernels:        # TMA needs 16-byte aligned operands: a clear rejection, not a fault
+            with pytest.raises(Q4KError):
+                q4k_q8_project(PrefillWeight(shifted_w[4:-4], w.scales, n, k), q, kernel=kern)
+        for kern in [L.KERNEL_AUTO] + [kk for kk in kernels_for(1) if kk not in tma_kernels]:
             base = q4k_q8_project(w, q, kernel=kern).cpu().numpy()[0]
             for variant in range(8):
                 ww = PrefillWeight(shifted_w[4:-4] if variant & 1 else w.codes,
@@ -226,7 +228,7 @@ def test_config0_single_gemv():
     assert hc.size + hs.size == 50135040
     w = PrefillWeight.from_host(hc, hs, 17408, 5120)
     x = synth.activations(1, 5120, seed=0)
-    run_and_check(w, hc, hs, x_f32=x, kernels=[L.KERNEL_AUTO, L.KERNEL_GEMV_DP4A, L.KERNEL_GEMV_MMA, L.KERNEL_MMA])
+    run_and_check(w, hc, hs, x_f32=x, kernels=[L.KERNEL_AUTO, L.KERNEL_GEMV_DP4A, L.KERNEL_GEMV_MMA, L.KERNEL_GEMV_TMA, L.KERNEL_MMA])
 
 
 @pytest.mark.parametrize("m", [1, 2, 4, 8, 16])
@@ -237,7 +239,7 @@ def test_config1_decode_projection_set(name, n, k, m):
     hc, hs = w.codes.cpu().numpy(), w.scales.cpu().numpy()
     xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=m))
     sample = [(0, 64), (n // 2 + 8, 40), (n - 72, 72)]
-    kernels = [L.KERNEL_AUTO, L.KERNEL_GEMV_MMA, L.KERNEL_TCGEN05] + ([L.KERNEL_MMA] if m <= 4 else [])
+    kernels = [L.KERNEL_AUTO, L.KERNEL_GEMV_MMA, L.KERNEL_GEMV_TMA, L.KERNEL_TCGEN05] + ([L.KERNEL_MMA] if m <= 4 else [])
     run_and_check(w, hc, hs, x_bits=xb, rows=sample, kernels=kernels, partial_rows=128)
 
 
@@ -304,6 +306,36 @@ def test_cluster_split_k_is_deterministic_and_exact(m, split_k, row_groups):
         assert (again.cpu().numpy() == y).all()
     with pytest.raises(Q4KError):
         q4k_q8_project(w, q, kernel=L.KERNEL_GEMV_MMA, split_k=9)
+
+
+@pytest.mark.parametrize("m,split_k,warps", [(1, 0, 0), (3, 1, 20), (7, 2, 0), (8, 3, 7), (8, 0, 5), (9, 0, 0), (13, 2, 12),
+                                             (16, 4, 0), (16, 20, 0)])
+def test_gemv_tma_plans(m, split_k, warps):
+    """Weights streamed by TMA, activations in registers: K slices of any width, ragged last slice,
+    odd number of row groups, partial dots bit-exact, two runs bitwise equal, status word clean."""
+    n, k = 1000, 5120                     # 125 row groups: the last 16-row tile is half outside the matrix
+    codes, meta = synth.logical_q4k(n, k, seed=6)
+    hc, hs = synth.split_tiles(codes, meta)
+    w = PrefillWeight.from_host(hc, hs, n, k)
+    xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=m))
+    q = pack_q8(bf16_tensor(xb), flag())
+    rz, ra, rs, _ = orc.q8_quantize(xb, bf16_bits=True)
+    ref = orc.project(hc, hs, n, k, rz, ra, rs)
+    part = torch.empty((m, n, 160), dtype=torch.int32, device=DEV)
+    res = dev(synth.activations(m, n, seed=4))
+    guarded = torch.full((m * n + 2,), -5.0, dtype=torch.float32, device=DEV)
+    y = q4k_q8_project(w, q, out=guarded[1:-1].view(m, n), kernel=L.KERNEL_GEMV_TMA, split_k=split_k,
+                       row_groups=warps, partials=part, residual=res).cpu().numpy()
+    assert guarded[0].item() == -5.0 and guarded[-1].item() == -5.0
+    assert_close_contract(y - res.cpu().numpy(), ref)
+    assert (part.cpu().numpy() == orc.dots(hc, n, k, rz)).all()
+    for _ in range(2):
+        again = q4k_q8_project(w, q, kernel=L.KERNEL_GEMV_TMA, split_k=split_k, row_groups=warps, residual=res)
+        assert (again.cpu().numpy() == y).all()
+    assert kernel_status() == 0
+    with pytest.raises(Q4KError):
+        q4k_q8_project(w, pack_q8(bf16_tensor(synth.f32_to_bf16_bits(synth.activations(17, k, seed=1))), flag()),
+                       kernel=L.KERNEL_GEMV_TMA)
 
 
 def ragged_offsets():
