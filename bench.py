@@ -163,6 +163,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill extra keys")
     ap.add_argument("--only", default="", help="debug: run a single part (decode)")
+    ap.add_argument("--no-overlap", action="store_true",
+                    help="launch every kernel fully serialised (no programmatic dependent launch)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
@@ -171,7 +173,7 @@ def main():
     import torch.distributed as dist
     from qw38_b200 import _lib as L
     from qw38_b200 import synth
-    from qw38_b200.q4k_q8 import new_q8_input, pack_q8, q4k_q8_project
+    from qw38_b200.q4k_q8 import new_q8_input, pack_q8, q4k_q8_project, set_launch_overlap
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -226,9 +228,9 @@ def main():
             dist.all_gather_into_tensor(gathered[(m, i)], outs[(m, i)])
 
     def which_kernel(m, rows):
-        """The library's own dispatch rule for m <= 16 (csrc/abi.cu): dp4a for one or two tokens
-        and for up to four on matrices of >= 32768 rows, cluster MMA otherwise."""
-        return "dp4a" if (m <= 2 or (m <= 4 and rows >= 32768)) else "mma"
+        """The library's own dispatch rule for m <= 16 and 16-byte aligned weights (csrc/abi.cu):
+        dp4a for one token, the TMA-streamed kernel for two to sixteen."""
+        return "dp4a" if m == 1 else "tma"
 
     def one_step(step, count=True, quantise=True, only_kernel=None):
         for mi, m in enumerate(TOKENS):
@@ -279,6 +281,10 @@ def main():
             ms = float(t.item())
         return ms
 
+    # The weights are final from here on, which is what the overlapped launches require.
+    torch.cuda.synchronize()
+    set_launch_overlap(not args.no_overlap)
+
     # A graph holds UNROLL steps so that the LAYERS weight copies are all visited.
     UNROLL = LAYERS
     use_graph = True
@@ -328,7 +334,7 @@ def main():
         hbm_peak, peak_src = (peaks["hbm_gbs"], "measured") if "hbm_gbs" in peaks else (6650.0, "fallback")
     # Per-kernel passes (all ranks take part so collectives match).
     per_kernel = {}
-    for kern in ("dp4a", "mma"):
+    for kern in ("dp4a", "tma"):
         pairs = [(m, i) for m in TOKENS for i in range(len(SHAPES)) if which_kernel(m, layers[0][i].n) == kern]
         fn = (lambda s, kk=kern: one_step(s, count=False, quantise=False, only_kernel=kk))
         gk = capture(fn, UNROLL) if use_graph else Eager(fn, UNROLL)
@@ -400,7 +406,7 @@ def main():
         dom = max(per_kernel, key=lambda kk: per_kernel[kk]["ms"])
         pkk = per_kernel[dom]
         achieved = pkk["GBps"]
-        kernel_name = {"dp4a": "gemv_dp4a_kernel", "mma": "gemv_mma_kernel"}[dom]
+        kernel_name = {"dp4a": "gemv_dp4a_kernel", "tma": "gemv_tma_kernel"}[dom]
         line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm_replays * UNROLL,
                 "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8 dot / fp32 affine", "data": "synthetic",
@@ -408,7 +414,8 @@ def main():
                                        "down 5120x17408, Q4_K weights, M in {1,2,4,8,16}, bf16 activations quantised on device",
                            "layers_rotated": LAYERS, "l2": f"weights rotate over {LAYERS} layer copies (1.49 GB) > 126 MB L2",
                            "parallelism": f"rows/{world}" + (" + NCCL all-gather" if world > 1 else ""),
-                           "launch": "CUDA graph replay" if use_graph else "eager",
+                           "launch": ("CUDA graph replay" if use_graph else "eager") +
+                                     ("" if args.no_overlap else ", programmatic dependent launch"),
                            "bytes_per_step": total_bytes},
                 "clocks": clocks, "gpu_launches": launches_per_step * steps,
                 "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -416,8 +423,8 @@ def main():
                 "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                              "frac": achieved / hbm_peak, "peak_source": peak_src,
                              # DRAM read+write of one launch = algorithmic bytes x the ratio measured by ncu on the
-                             # 34816x5120 captures under profiles/ (1.034 cluster MMA at M=8, 1.033 dp4a at M=1)
-                             "traffic": pkk["bytes_per_launch"] * (1.034 if dom == "mma" else 1.033),
+                             # 34816x5120 captures under profiles/ (1.034 TMA kernel at M=8, 1.033 dp4a at M=1)
+                             "traffic": pkk["bytes_per_launch"] * (1.034 if dom == "tma" else 1.033),
                              "avg_launch_us": pkk["avg_us"], "bytes_per_launch": pkk["bytes_per_launch"],
                              "by_kernel": {kk: {"GBps": round(v["GBps"], 1), "frac": round(v["GBps"] / hbm_peak, 4),
                                                 "avg_us": round(v["avg_us"], 3), "launches": v["launches"]}

@@ -93,6 +93,19 @@ const char* q4k_last_error(void);   /* thread-local text of the last failure */
 int q4k_last_cuda_status(void);     /* cudaError_t of the last Q4K_ERR_STATUS */
 uint32_t q4k_abi_version(void);
 
+/* Programmatic dependent launch for the decode path (no counterpart in the reference, which
+ * replays its decode step as a CUDA graph of fully serialised kernels, src/runtime/language_model.cpp:324-356).
+ * When enabled (process-wide, default off), q4k_pack_q8_*, and q4k_q8_project* for m <= 16 launch
+ * their kernels so that they may begin while the preceding kernel of the stream is still draining:
+ * blocks are placed as SMs free up, and the TMA kernel streams WEIGHT tiles into shared memory
+ * before it waits for that kernel.  Activations, residual, output and scratch are touched only
+ * after the preceding kernel has completed, so results are unchanged.  The caller's side of the
+ * contract: no work still in flight earlier in the stream writes the weight operand (true for
+ * decode, where weights are constant; leave it off around q4k_repack_blocks144 or uploads).
+ * Works inside CUDA graph capture. */
+void q4k_set_launch_overlap(int enabled);
+int q4k_get_launch_overlap(void);
+
 /* Synchronises the current device and reads the status word of the tcgen05 kernel (library-owned
  * scratch): 0 = every launch so far ran to completion; nonzero = a bounded wait inside the
  * kernel gave up at that site and the affected block returned without writing its outputs.

@@ -43,6 +43,8 @@ SIGNATURES = {
     "q4k_last_cuda_status": (_i, []),
     "q4k_abi_version": (_u32, []),
     "q4k_kernel_status": (_i, [C.POINTER(_i)]),
+    "q4k_set_launch_overlap": (None, [_i]),
+    "q4k_get_launch_overlap": (_i, []),
     "q4k_pad_n": (_u64, [_u32]),
     "q4k_pad_k": (_u32, [_u32]),
     "q4k_code_bytes": (_u64, [_u32, _u32]),

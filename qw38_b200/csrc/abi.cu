@@ -12,6 +12,7 @@
 #include <cstdio>
 #include <cstring>
 #include <limits>
+#include <atomic>
 #include <mutex>
 
 #include "../../include/q4k_b200.h"
@@ -189,9 +190,11 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
 
   uint32_t kernel = opt ? opt->kernel : Q4K_KERNEL_AUTO;
   if (kernel == Q4K_KERNEL_AUTO) {
-    // dp4a for one or two tokens (and up to four on very tall matrices, where it measured
-    // faster), cluster MMA up to 16 tokens, tcgen05 beyond when TMA alignment allows.
-    if (x.m <= 2 || (x.m <= q4k::kGemvDp4aMaxTokens && w.padded_n >= 32768)) kernel = Q4K_KERNEL_GEMV_DP4A;
+    // One token: dp4a.  Two to sixteen: the TMA-streamed kernel when the weights are 16-byte
+    // aligned, else dp4a / cluster MMA.  Beyond: tcgen05 when TMA alignment allows.
+    if (x.m == 1) kernel = Q4K_KERNEL_GEMV_DP4A;
+    else if (x.m <= q4k::kGemvTmaMaxTokens && q4k::gemv_tma_supported(view(w), view(x))) kernel = Q4K_KERNEL_GEMV_TMA;
+    else if (x.m <= 2 || (x.m <= q4k::kGemvDp4aMaxTokens && w.padded_n >= 32768)) kernel = Q4K_KERNEL_GEMV_DP4A;
     else if (x.m <= 16) kernel = Q4K_KERNEL_GEMV_MMA;
     else kernel = q4k::tcgen05_supported(view(w), view(x)) ? Q4K_KERNEL_TCGEN05 : Q4K_KERNEL_MMA;
   }
@@ -303,7 +306,11 @@ int pack_impl(const void* input, bool fp32, uint64_t input_len, const q4k_q8_inp
 
 }  // namespace
 
+namespace {
+std::atomic<bool> g_launch_overlap{false};
+}
 namespace q4k {
+bool launch_overlap() { return g_launch_overlap.load(std::memory_order_relaxed); }
 int set_error(int code, const char* fmt, ...) {
   va_list ap;
   va_start(ap, fmt);
@@ -319,6 +326,9 @@ extern "C" {
 const char* q4k_last_error(void) { return g_error; }
 int q4k_last_cuda_status(void) { return g_cuda_status; }
 uint32_t q4k_abi_version(void) { return 1; }
+
+void q4k_set_launch_overlap(int enabled) { g_launch_overlap.store(enabled != 0, std::memory_order_relaxed); }
+int q4k_get_launch_overlap(void) { return g_launch_overlap.load(std::memory_order_relaxed) ? 1 : 0; }
 
 uint64_t q4k_pad_n(uint32_t n) { return n == 0 ? 0 : (uint64_t(n) + 7) / 8 * 8; }
 uint32_t q4k_pad_k(uint32_t k) { return k == 0 ? 0 : (k + 255u) / 256u * 256u; }

@@ -60,4 +60,13 @@ __device__ __forceinline__ uint32_t byte_of(uint32_t w, uint32_t i) { return (w 
 __device__ __forceinline__ uint32_t even_bytes(uint32_t z0, uint32_t z1) { return __byte_perm(z0, z1, 0x6420); }
 __device__ __forceinline__ uint32_t odd_bytes(uint32_t z0, uint32_t z1) { return __byte_perm(z0, z1, 0x7531); }
 
+// Programmatic dependent launch.  A kernel launched with the stream-serialization attribute may
+// start while the kernel before it in the stream is still running; it must call pdl_wait()
+// before it reads anything that kernel may have written and before it writes global memory.
+// pdl_launch_dependents() tells the scheduler that the next kernel in the stream may start as
+// soon as every block of this grid has called it (or exited).  Both are no-ops for kernels
+// launched without the attribute.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 }  // namespace q4k

@@ -71,6 +71,8 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(WeightView w, Q8Vie
                                                              const float* __restrict__ residual,
                                                              int32_t* __restrict__ partials, uint32_t rgc, bool wide) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();  // activations (and the residual) may come from the kernel before this one
   uint32_t const pk = x.padded_k, G = pk / 32, tiles_k = w.tiles_k;
   uint8_t* const zs = smem;
   float* const as = reinterpret_cast<float*>(smem + size_t(M) * tiles_k * kActKb);
@@ -219,7 +221,7 @@ cudaError_t launch_m(const WeightView& w, const Q8View& x, float* out, const flo
     cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
     if (st != cudaSuccess) return st;
   }
-  kernel<<<grid, kThreads, smem, stream>>>(w, x, out, residual, partials, rgc, wide);
+  return launch_kernel(kernel, grid, kThreads, smem, stream, launch_overlap(), w, x, out, residual, partials, rgc, wide);
   return cudaGetLastError();
 }
 

@@ -137,6 +137,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
   uint32_t const t1 = min(p.row_tiles, t0 + p.tiles_per_range);
   uint32_t const ntiles = t1 > t0 ? t1 - t0 : 0;
 
+  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < stages; ++s) {
       mbar_init(b_full + 8 * s, 1);
@@ -152,6 +153,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
   }
   __syncthreads();
 
+  // The producer streams weights at once: they are constant, whatever kernel runs before this
+  // one.  Every other role first waits for the preceding kernel of the stream, because the
+  // activations, the residual, the output and the split-K scratch may be its to write.
   if (warp == kProducer) {
     if (lane == 0) {
       uint32_t s = 0, ph = 1;  // the first pass over the ring finds every stage free
@@ -168,6 +172,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     // Adds the consumers' 16 x (8*NT) tiles in warp order.  Lane (r = lane/4, q = lane%4) owns
     // rows r, r+8 and tokens 2q, 2q+1 of every octet -- the MMA accumulator layout.
     uint32_t const r = lane >> 2, q = lane & 3;
+    pdl_wait();
     float* const dst = p.split_k > 1 ? p.slices + size_t(slice) * p.m * p.n : p.out;
     bool const add_residual = p.split_k == 1 && p.residual != nullptr;
     for (uint32_t it = 0; it < ntiles; ++it) {
@@ -206,6 +211,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
   } else if (warp - kFirstConsumer < nact) {
     uint32_t const w = warp - kFirstConsumer, sb = sb0 + w;
     uint32_t const r = lane >> 2, q = lane & 3;
+    pdl_wait();
     // ---- K-stationary operands ----
     uint32_t const tab = s_tab + w * tab_bytes;
     // activation scale pairs {a[2q], a[2q+1]} of (octet nt, group g) at ((nt*4 + g/2)*4 + q)*16 + (g%2)*8
@@ -264,9 +270,15 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     uint32_t s = 0, ph = 0, code_off = 0, meta_off = 0;
     for (uint32_t it = 0; it < ntiles; ++it) {
       if (!mbar_wait(b_full + 8 * s, ph, abort_flag, p.status, 0x530)) break;
+      // ---- pull this warp's part of the stage into registers and give the stage back at once ----
+      uint32_t raw[4][4];
+      uint32_t const cbase = ld_base + code_off;
+#pragma unroll
+      for (int gp = 0; gp < 4; ++gp) ldmatrix_x4(raw[gp], cbase + ((uint32_t(gp) << 5) ^ ld_x));
+      uint4 const mw = lds128(dec_meta + meta_off);
+      mbar_arrive(b_empty + 8 * s);  // release semantics: the loads above are performed before the arrival
       // ---- decode the metadata of 16 rows ----
       {
-        uint4 const mw = lds128(dec_meta + meta_off);
         uint32_t const sc4 = ((mw.y >> dsh) & dmask_a) | (mw.w & dmask_b);
         uint32_t const mn4 = ((mw.z >> dsh) & dmask_a) | ((mw.w >> 4) & dmask_b);
         float const s0 = float(sc4 & 0xffu), s1 = float((sc4 >> 8) & 0xffu), s2 = float((sc4 >> 16) & 0xffu), s3 = float(sc4 >> 24);
@@ -285,11 +297,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
 #pragma unroll
         for (int j = 0; j < 4; ++j) mins[nt][j] = 0.f;
       }
-      uint32_t const cbase = ld_base + code_off;
 #pragma unroll
       for (int gp = 0; gp < 4; ++gp) {
-        uint32_t raw[4];
-        ldmatrix_x4(raw, cbase + ((uint32_t(gp) << 5) ^ ld_x));
         float4 const sc_lo = lds128f(rd_sc + gp * 16);         // row r:   {s_g, s_g, s_g+1, s_g+1}
         float4 const sc_hi = lds128f(rd_sc + 640 + gp * 16);   // row r+8
         float4 ap4[NT];
@@ -298,7 +307,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           int const g = gp * 2 + e;
-          uint32_t const w0 = raw[2 * e], w1 = raw[2 * e + 1];
+          uint32_t const w0 = raw[gp][2 * e], w1 = raw[gp][2 * e + 1];
           uint32_t const a0 = w0 & 0x0f0f0f0fu, a1 = w1 & 0x0f0f0f0fu;
           uint32_t const a2 = (w0 >> 4) & 0x0f0f0f0fu, a3 = (w1 >> 4) & 0x0f0f0f0fu;
           float2 const s_lo = e ? make_float2(sc_lo.z, sc_lo.w) : make_float2(sc_lo.x, sc_lo.y);
@@ -334,7 +343,6 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       }
       float4 const dd_lo = lds128f(rd_dd);        // {d, d, -dmin, -dmin} of row r
       float4 const dd_hi = lds128f(rd_dd + 128);  // row r+8
-      mbar_arrive(b_empty + 8 * s);  // this lane has consumed its part of the stage's code and metadata tiles
       // ---- hand the tile to the reducer ----
       uint32_t const rs = two_slots ? it & 1 : 0, ruse = two_slots ? it >> 1 : it;
       if (ruse > 0 && !mbar_wait(b_rempty + 8 * rs, (ruse - 1) & 1, abort_flag, p.status, 0x540)) break;
@@ -356,6 +364,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
 
   // ---- split-K: the last block of a row range adds the slices in order ----
   if (p.split_k > 1) {
+    pdl_wait();
     __syncthreads();
     if (threadIdx.x == 0) {
       __threadfence();
@@ -395,8 +404,7 @@ cudaError_t launch_cfg(const CUtensorMap& tm_codes, const CUtensorMap& tm_meta, 
   auto kernel = dump ? gemv_tma_kernel<NT, MAXW, true> : gemv_tma_kernel<NT, MAXW, false>;
   cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (st != cudaSuccess) return st;
-  kernel<<<grid, (p.cw + kFirstConsumer) * 32, smem, stream>>>(tm_codes, tm_meta, p);
-  return cudaGetLastError();
+  return launch_kernel(kernel, grid, (p.cw + kFirstConsumer) * 32, smem, stream, launch_overlap(), tm_codes, tm_meta, p);
 }
 
 }  // namespace

@@ -85,6 +85,28 @@ GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
 cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
                             const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream);
 
+// abi.cu : process-wide switch set by q4k_set_launch_overlap().  When on, the decode kernels
+// (pack, dp4a, TMA gemv) are launched with programmatic stream serialization: they may start,
+// and the TMA kernel may prefetch weights, while the preceding kernel of the stream drains.
+bool launch_overlap();
+
+// Launch with or without the programmatic-stream-serialization attribute.
+template <typename... KArgs, typename... Args>
+cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                          bool overlap, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = overlap ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 // abi.cu : records the thread-local error text behind q4k_last_error() and returns `code`.
 int set_error(int code, const char* fmt, ...);
 int set_error_cuda(cudaError_t status, const char* operation);

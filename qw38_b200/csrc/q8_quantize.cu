@@ -70,6 +70,8 @@ template <typename T, bool Vec>
 __global__ void __launch_bounds__(kThreads) pack_kernel(const T* __restrict__ in, int8_t* codes,
                                                          float* scales, int32_t* sums, uint32_t m,
                                                          uint32_t k, uint32_t pk, int* failure) {
+  pdl_launch_dependents();  // the projection that follows may start prefetching its weights
+  pdl_wait();               // the input may come from the kernel before this one
   uint32_t const lane = threadIdx.x & 31, sub = lane & 3, grp = lane >> 2;
   uint64_t const chunks_row = pk / 256;
   uint64_t const tasks = uint64_t(m) * chunks_row;
@@ -213,12 +215,12 @@ cudaError_t launch_pack_q8(const void* input, bool fp32, Q8Out out, uint32_t k, 
   bool const vec = (k % 8 == 0) && (reinterpret_cast<uintptr_t>(input) % 16 == 0);
   if (fp32) {
     auto* in = static_cast<const float*>(input);
-    if (vec) pack_kernel<float, true><<<grid, kThreads, 0, stream>>>(in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
-    else pack_kernel<float, false><<<grid, kThreads, 0, stream>>>(in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
+    if (vec) return launch_kernel(pack_kernel<float, true>, grid, kThreads, 0, stream, launch_overlap(), in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
+    else return launch_kernel(pack_kernel<float, false>, grid, kThreads, 0, stream, launch_overlap(), in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
   } else {
     auto* in = static_cast<const uint16_t*>(input);
-    if (vec) pack_kernel<uint16_t, true><<<grid, kThreads, 0, stream>>>(in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
-    else pack_kernel<uint16_t, false><<<grid, kThreads, 0, stream>>>(in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
+    if (vec) return launch_kernel(pack_kernel<uint16_t, true>, grid, kThreads, 0, stream, launch_overlap(), in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
+    else return launch_kernel(pack_kernel<uint16_t, false>, grid, kThreads, 0, stream, launch_overlap(), in, out.codes, out.scales, out.sums, out.m, k, out.padded_k, failure);
   }
   return cudaGetLastError();
 }

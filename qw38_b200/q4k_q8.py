@@ -27,6 +27,16 @@ def _check(status: int) -> None:
         raise Q4KError(status, L.load().q4k_last_error().decode())
 
 
+def set_launch_overlap(enabled: bool) -> None:
+    """Process-wide switch (q4k_set_launch_overlap): decode kernels may start, and stream weight tiles,
+    while the preceding kernel of the stream drains.  Only while nothing in flight writes the weights."""
+    L.load().q4k_set_launch_overlap(1 if enabled else 0)
+
+
+def launch_overlap() -> bool:
+    return bool(L.load().q4k_get_launch_overlap())
+
+
 def pad_n(n: int) -> int:
     return (n + 7) // 8 * 8
 

@@ -338,6 +338,60 @@ def test_gemv_tma_plans(m, split_k, warps):
                        kernel=L.KERNEL_GEMV_TMA)
 
 
+def test_launch_overlap_gives_identical_results():
+    """Programmatic dependent launch: kernels start (and the TMA kernel streams weights) while the one
+    before drains.  A chain pack -> four projections per token count, eager and as a CUDA graph, must
+    reproduce the serialised results bit for bit, split-K scratch and tickets included."""
+    from qw38_b200 import set_launch_overlap, launch_overlap
+    shapes = [(1000, 5120), (520, 5120), (2048, 5120), (512, 17408)]     # the last one splits K four ways
+    ws = [synth.device_weight(n, k, seed=40 + i) for i, (n, k) in enumerate(shapes)]
+    xs = {m: {k: bf16_tensor(synth.f32_to_bf16_bits(synth.activations(m, k, seed=m + k))) for k in (5120, 17408)}
+          for m in (1, 3, 8, 16)}
+    f = flag()
+    qs = {m: {k: new_q8_input(m, k) for k in (5120, 17408)} for m in xs}
+    outs = {(m, i): torch.empty((m, n), dtype=torch.float32, device=DEV) for m in xs for i, (n, _) in enumerate(shapes)}
+
+    def chain():
+        for m in xs:
+            for k in (5120, 17408):
+                pack_q8(xs[m][k], f, out=qs[m][k])
+            for i, (n, k) in enumerate(shapes):
+                q4k_q8_project(ws[i], qs[m][k], out=outs[(m, i)], trusted=True)
+
+    assert not launch_overlap()
+    chain()
+    torch.cuda.synchronize()
+    want = {key: t.clone() for key, t in outs.items()}
+    try:
+        set_launch_overlap(True)
+        assert launch_overlap()
+        for t in outs.values():
+            t.fill_(-3.0)
+        for _ in range(3):
+            chain()
+        torch.cuda.synchronize()
+        for key in outs:
+            assert torch.equal(outs[key], want[key]), f"eager overlap differs at {key}"
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            chain()
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                chain()
+                chain()
+            for t in outs.values():
+                t.fill_(-3.0)
+            for _ in range(3):
+                g.replay()
+            stream.synchronize()
+        for key in outs:
+            assert torch.equal(outs[key], want[key]), f"graph overlap differs at {key}"
+    finally:
+        set_launch_overlap(False)
+    assert f.item() == 0 and kernel_status() == 0
+
+
 def ragged_offsets():
     lens = [1] * 48 + [512, 237, 1024]
     return np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
