@@ -229,8 +229,9 @@ def main():
 
     def which_kernel(m, rows):
         """The library's own dispatch rule for m <= 16 and 16-byte aligned weights (csrc/abi.cu):
-        dp4a for one token, the TMA-streamed kernel for two to sixteen."""
-        return "dp4a" if m == 1 else "tma"
+        the TMA-streamed kernel for two to sixteen tokens, and for one token too when launches overlap;
+        dp4a for one token otherwise."""
+        return "dp4a" if (m == 1 and args.no_overlap) else "tma"
 
     def one_step(step, count=True, quantise=True, only_kernel=None):
         for mi, m in enumerate(TOKENS):
@@ -336,6 +337,8 @@ def main():
     per_kernel = {}
     for kern in ("dp4a", "tma"):
         pairs = [(m, i) for m in TOKENS for i in range(len(SHAPES)) if which_kernel(m, layers[0][i].n) == kern]
+        if not pairs:
+            continue
         fn = (lambda s, kk=kern: one_step(s, count=False, quantise=False, only_kernel=kk))
         gk = capture(fn, UNROLL) if use_graph else Eager(fn, UNROLL)
         timed(gk, warm_replays)

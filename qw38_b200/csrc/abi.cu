@@ -190,10 +190,12 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
 
   uint32_t kernel = opt ? opt->kernel : Q4K_KERNEL_AUTO;
   if (kernel == Q4K_KERNEL_AUTO) {
-    // One token: dp4a.  Two to sixteen: the TMA-streamed kernel when the weights are 16-byte
-    // aligned, else dp4a / cluster MMA.  Beyond: tcgen05 when TMA alignment allows.
-    if (x.m == 1) kernel = Q4K_KERNEL_GEMV_DP4A;
-    else if (x.m <= q4k::kGemvTmaMaxTokens && q4k::gemv_tma_supported(view(w), view(x))) kernel = Q4K_KERNEL_GEMV_TMA;
+    // Up to sixteen tokens: the TMA-streamed kernel when the weights are 16-byte aligned (for a
+    // single token only with overlapped launches, where its early weight prefetch pays; serialised,
+    // dp4a measured a little faster there), else dp4a / cluster MMA.  Beyond: tcgen05 when TMA
+    // alignment allows.
+    bool const tma_ok = x.m <= q4k::kGemvTmaMaxTokens && q4k::gemv_tma_supported(view(w), view(x));
+    if (tma_ok && (x.m >= 2 || q4k::launch_overlap())) kernel = Q4K_KERNEL_GEMV_TMA;
     else if (x.m <= 2 || (x.m <= q4k::kGemvDp4aMaxTokens && w.padded_n >= 32768)) kernel = Q4K_KERNEL_GEMV_DP4A;
     else if (x.m <= 16) kernel = Q4K_KERNEL_GEMV_MMA;
     else kernel = q4k::tcgen05_supported(view(w), view(x)) ? Q4K_KERNEL_TCGEN05 : Q4K_KERNEL_MMA;

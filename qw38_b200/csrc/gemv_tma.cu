@@ -35,7 +35,7 @@ namespace {
 
 constexpr uint32_t kMagicI = 0x4B400000u;  // bit pattern of 1.5 * 2^23
 constexpr float kMagicF = 12582912.0f;
-constexpr int kProducer = 0, kReducer = 1, kFirstConsumer = 2;
+constexpr int kProducer = 0, kFirstReducer = 1;  // then NT reducer warps, then the consumers
 // per consumer warp: 1280 scale pairs (16 rows, stride 80 bytes so that the eight rows a load touches fall in
 // different banks), 768 mins (row stride 12 floats), 256 d/dmin, then NT * 256 activation scale pairs
 constexpr int kTabBytes = 2304, kTabMn = 1280, kTabDd = 2048;
@@ -128,8 +128,9 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
   volatile int* const abort_flag = flags;
   int* const last_flag = flags + 1;
 
+  constexpr uint32_t kFirstConsumer = kFirstReducer + NT;
   uint32_t const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  bool const two_slots = p.red_slots == 2;
+  uint32_t const slot_mask = p.red_slots - 1, slot_shift = p.red_slots - 1;  // red_slots is 1 or 2
   uint32_t const range = blockIdx.x / p.split_k, slice = blockIdx.x % p.split_k;
   uint32_t const sb0 = slice * cw;
   uint32_t const nact = min(cw, p.tiles_k - sb0);  // consumer warps with a real super-block
@@ -145,7 +146,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     }
     for (uint32_t s = 0; s < 2; ++s) {
       mbar_init(b_rfull + 8 * s, nact * 32);
-      mbar_init(b_rempty + 8 * s, 32);
+      mbar_init(b_rempty + 8 * s, 32 * NT);
     }
     *abort_flag = 0;
     *last_flag = 0;
@@ -168,43 +169,38 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         if (++s == stages) { s = 0; ph ^= 1; }
       }
     }
-  } else if (warp == kReducer) {
-    // Adds the consumers' 16 x (8*NT) tiles in warp order.  Lane (r = lane/4, q = lane%4) owns
-    // rows r, r+8 and tokens 2q, 2q+1 of every octet -- the MMA accumulator layout.
+  } else if (warp < kFirstConsumer) {
+    // One reducer warp per token octet adds the consumers' 16 x 8 tiles in warp order.  Lane
+    // (r = lane/4, q = lane%4) owns rows r, r+8 and tokens 2q, 2q+1 -- the MMA accumulator layout.
+    uint32_t const nt = warp - kFirstReducer;
     uint32_t const r = lane >> 2, q = lane & 3;
     pdl_wait();
     float* const dst = p.split_k > 1 ? p.slices + size_t(slice) * p.m * p.n : p.out;
-    bool const add_residual = p.split_k == 1 && p.residual != nullptr;
+    const float* const res = p.split_k == 1 ? p.residual : nullptr;
+    uint32_t const tok0 = nt * 8 + q * 2;
+    bool const live0 = tok0 < p.m, live1 = tok0 + 1 < p.m;
+    size_t const o0 = size_t(tok0) * p.n, o1 = o0 + p.n;
     for (uint32_t it = 0; it < ntiles; ++it) {
-      uint32_t const s = two_slots ? it & 1 : 0, use = two_slots ? it >> 1 : it;
+      uint32_t const s = it & slot_mask, use = it >> slot_shift;
       if (!mbar_wait(b_rfull + 8 * s, use & 1, abort_flag, p.status, 0x520)) break;
-      float4 acc[NT];
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) acc[nt] = make_float4(0.f, 0.f, 0.f, 0.f);
-      uint32_t src = s_red + s * red_slot + lane * 16;
+      float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+      uint32_t src = s_red + s * red_slot + nt * 512 + lane * 16;
+#pragma unroll 4
       for (uint32_t w = 0; w < nact; ++w) {
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          float4 const v = lds128f(src + nt * 512);
-          acc[nt].x += v.x; acc[nt].y += v.y; acc[nt].z += v.z; acc[nt].w += v.w;
-        }
+        float4 const v = lds128f(src);
+        lo = __fadd2_rn(lo, make_float2(v.x, v.y));
+        hi = __fadd2_rn(hi, make_float2(v.z, v.w));
         src += NT * 512;
       }
       mbar_arrive(b_rempty + 8 * s);
       uint32_t const row = (t0 + it) * 16 + r;
-#pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        float const v[4] = {acc[nt].x, acc[nt].y, acc[nt].z, acc[nt].w};
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          uint32_t const tok = nt * 8 + q * 2 + (j & 1), rr = row + (j >> 1) * 8;
-          if (tok < p.m && rr < p.n) {
-            size_t const o = size_t(tok) * p.n + rr;
-            float val = v[j];
-            if (add_residual) val += p.residual[o];
-            dst[o] = val;
-          }
-        }
+      if (row < p.n) {
+        if (live0) dst[o0 + row] = lo.x + (res ? res[o0 + row] : 0.f);
+        if (live1) dst[o1 + row] = lo.y + (res ? res[o1 + row] : 0.f);
+      }
+      if (row + 8 < p.n) {
+        if (live0) dst[o0 + row + 8] = hi.x + (res ? res[o0 + row + 8] : 0.f);
+        if (live1) dst[o1 + row + 8] = hi.y + (res ? res[o1 + row + 8] : 0.f);
       }
     }
     __threadfence();
@@ -270,21 +266,24 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     uint32_t s = 0, ph = 0, code_off = 0, meta_off = 0;
     for (uint32_t it = 0; it < ntiles; ++it) {
       if (!mbar_wait(b_full + 8 * s, ph, abort_flag, p.status, 0x530)) break;
-      // ---- pull this warp's part of the stage into registers and give the stage back at once ----
-      uint32_t raw[4][4];
       uint32_t const cbase = ld_base + code_off;
-#pragma unroll
-      for (int gp = 0; gp < 4; ++gp) ldmatrix_x4(raw[gp], cbase + ((uint32_t(gp) << 5) ^ ld_x));
       uint4 const mw = lds128(dec_meta + meta_off);
-      mbar_arrive(b_empty + 8 * s);  // release semantics: the loads above are performed before the arrival
       // ---- decode the metadata of 16 rows ----
       {
         uint32_t const sc4 = ((mw.y >> dsh) & dmask_a) | (mw.w & dmask_b);
         uint32_t const mn4 = ((mw.z >> dsh) & dmask_a) | ((mw.w >> 4) & dmask_b);
-        float const s0 = float(sc4 & 0xffu), s1 = float((sc4 >> 8) & 0xffu), s2 = float((sc4 >> 16) & 0xffu), s3 = float(sc4 >> 24);
-        sts128f(dec_sc, s0, s0, s1, s1);
-        sts128f(dec_sc + 16, s2, s2, s3, s3);
-        sts128f(dec_mn, float(mn4 & 0xffu), float((mn4 >> 8) & 0xffu), float((mn4 >> 16) & 0xffu), float(mn4 >> 24));
+        // byte -> float without shifts: splice the byte under the exponent of 2^23 (PRMT), then one
+        // packed subtraction per pair of values; scales are stored twice, as the packed FMAs read them
+        float2 const m23 = make_float2(-8388608.0f, -8388608.0f);
+        uint32_t const e0 = __byte_perm(sc4, 0x4b000000u, 0x7650), e1 = __byte_perm(sc4, 0x4b000000u, 0x7651);
+        uint32_t const e2 = __byte_perm(sc4, 0x4b000000u, 0x7652), e3 = __byte_perm(sc4, 0x4b000000u, 0x7653);
+        float2 const p0 = __fadd2_rn(as_f2(e0, e0), m23), p1 = __fadd2_rn(as_f2(e1, e1), m23);
+        float2 const p2 = __fadd2_rn(as_f2(e2, e2), m23), p3 = __fadd2_rn(as_f2(e3, e3), m23);
+        sts128f(dec_sc, p0.x, p0.y, p1.x, p1.y);
+        sts128f(dec_sc + 16, p2.x, p2.y, p3.x, p3.y);
+        float2 const q0 = __fadd2_rn(as_f2(__byte_perm(mn4, 0x4b000000u, 0x7650), __byte_perm(mn4, 0x4b000000u, 0x7651)), m23);
+        float2 const q1 = __fadd2_rn(as_f2(__byte_perm(mn4, 0x4b000000u, 0x7652), __byte_perm(mn4, 0x4b000000u, 0x7653)), m23);
+        sts128f(dec_mn, q0.x, q0.y, q1.x, q1.y);
         float const d = fp16_bits_to_f32(mw.x & 0xffffu), ndmin = -fp16_bits_to_f32(mw.x >> 16);
         sts128f(dec_dd, d, d, ndmin, ndmin);  // both halves of a row store the same words
       }
@@ -299,6 +298,11 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       }
 #pragma unroll
       for (int gp = 0; gp < 4; ++gp) {
+        uint32_t raw[4];
+        ldmatrix_x4(raw, cbase + ((uint32_t(gp) << 5) ^ ld_x));
+        // The stage goes back to the producer as soon as its last word is in registers (the arrival has
+        // release semantics, so the loads above are performed before it).
+        if (gp == 3) mbar_arrive(b_empty + 8 * s);
         float4 const sc_lo = lds128f(rd_sc + gp * 16);         // row r:   {s_g, s_g, s_g+1, s_g+1}
         float4 const sc_hi = lds128f(rd_sc + 640 + gp * 16);   // row r+8
         float4 ap4[NT];
@@ -307,7 +311,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           int const g = gp * 2 + e;
-          uint32_t const w0 = raw[gp][2 * e], w1 = raw[gp][2 * e + 1];
+          uint32_t const w0 = raw[2 * e], w1 = raw[2 * e + 1];
           uint32_t const a0 = w0 & 0x0f0f0f0fu, a1 = w1 & 0x0f0f0f0fu;
           uint32_t const a2 = (w0 >> 4) & 0x0f0f0f0fu, a3 = (w1 >> 4) & 0x0f0f0f0fu;
           float2 const s_lo = e ? make_float2(sc_lo.z, sc_lo.w) : make_float2(sc_lo.x, sc_lo.y);
@@ -344,7 +348,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       float4 const dd_lo = lds128f(rd_dd);        // {d, d, -dmin, -dmin} of row r
       float4 const dd_hi = lds128f(rd_dd + 128);  // row r+8
       // ---- hand the tile to the reducer ----
-      uint32_t const rs = two_slots ? it & 1 : 0, ruse = two_slots ? it >> 1 : it;
+      uint32_t const rs = it & slot_mask, ruse = it >> slot_shift;
       if (ruse > 0 && !mbar_wait(b_rempty + 8 * rs, (ruse - 1) & 1, abort_flag, p.status, 0x540)) break;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
@@ -404,7 +408,7 @@ cudaError_t launch_cfg(const CUtensorMap& tm_codes, const CUtensorMap& tm_meta, 
   auto kernel = dump ? gemv_tma_kernel<NT, MAXW, true> : gemv_tma_kernel<NT, MAXW, false>;
   cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (st != cudaSuccess) return st;
-  return launch_kernel(kernel, grid, (p.cw + kFirstConsumer) * 32, smem, stream, launch_overlap(), tm_codes, tm_meta, p);
+  return launch_kernel(kernel, grid, (p.cw + kFirstReducer + NT) * 32, smem, stream, launch_overlap(), tm_codes, tm_meta, p);
 }
 
 }  // namespace
@@ -418,9 +422,14 @@ GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
   GemvTmaPlan p;
   uint32_t const nt = m <= 8 ? 1 : 2;
   uint32_t const max_cw = nt == 1 ? kGemvTmaMaxWarpsNarrow : kGemvTmaMaxWarpsWide;
+  uint32_t const row_tiles = ((n + 7) / 8 * 8 + 15) / 16;
   uint32_t split = split_k_request;
   if (split == 0) {
-    uint32_t const cw_target = warps_request ? (warps_request < max_cw ? warps_request : max_cw) : max_cw;
+    // Widest K slice by default.  Sixteen tokens on a matrix with few row tiles per SM measured faster
+    // with narrower slices (more, shorter blocks in flight and twice the registers per thread).
+    uint32_t cw_target = max_cw;
+    if (nt == 2 && row_tiles < 1024) cw_target = 12;
+    if (warps_request) cw_target = warps_request < max_cw ? warps_request : max_cw;
     split = (tiles_k + cw_target - 1) / cw_target;
   }
   if (split > tiles_k) split = tiles_k;
@@ -430,7 +439,6 @@ GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
   split = (tiles_k + cw - 1) / cw;  // drop empty slices
   p.split_k = split;
   p.warps = cw;
-  uint32_t const row_tiles = ((n + 7) / 8 * 8 + 15) / 16;
   uint32_t ranges = uint32_t(sm_count()) / split;
   if (ranges < 1) ranges = 1;
   if (ranges > row_tiles) ranges = row_tiles;
@@ -479,8 +487,8 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
     if (cw <= 12) return launch_cfg<1, 14>(tm_codes, tm_meta, p, dump, grid, smem, stream);
     return launch_cfg<1, kGemvTmaMaxWarpsNarrow + 2>(tm_codes, tm_meta, p, dump, grid, smem, stream);
   }
-  if (cw <= 12) return launch_cfg<2, 14>(tm_codes, tm_meta, p, dump, grid, smem, stream);
-  return launch_cfg<2, kGemvTmaMaxWarpsWide + 2>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+  if (cw <= 12) return launch_cfg<2, 15>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+  return launch_cfg<2, kGemvTmaMaxWarpsWide + 3>(tm_codes, tm_meta, p, dump, grid, smem, stream);
 }
 
 }  // namespace q4k

@@ -349,14 +349,18 @@ def test_launch_overlap_gives_identical_results():
           for m in (1, 3, 8, 16)}
     f = flag()
     qs = {m: {k: new_q8_input(m, k) for k in (5120, 17408)} for m in xs}
-    outs = {(m, i): torch.empty((m, n), dtype=torch.float32, device=DEV) for m in xs for i, (n, _) in enumerate(shapes)}
+    # explicit kernels: automatic dispatch of a single token depends on the switch under test
+    kerns = {m: [L.KERNEL_GEMV_TMA] + ([L.KERNEL_GEMV_DP4A] if m <= 4 else []) for m in xs}
+    outs = {(m, i, kern): torch.empty((m, n), dtype=torch.float32, device=DEV)
+            for m in xs for i, (n, _) in enumerate(shapes) for kern in kerns[m]}
 
     def chain():
         for m in xs:
             for k in (5120, 17408):
                 pack_q8(xs[m][k], f, out=qs[m][k])
             for i, (n, k) in enumerate(shapes):
-                q4k_q8_project(ws[i], qs[m][k], out=outs[(m, i)], trusted=True)
+                for kern in kerns[m]:
+                    q4k_q8_project(ws[i], qs[m][k], out=outs[(m, i, kern)], kernel=kern, trusted=True)
 
     assert not launch_overlap()
     chain()
