@@ -163,6 +163,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill extra keys")
     ap.add_argument("--only", default="", help="debug: run a single part (decode)")
+    ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
+                    help="N > 1: projection kernels store into every rank's output over NVLink (fused), or "
+                         "NCCL all-gather after each projection")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch every kernel fully serialised (no programmatic dependent launch)")
     args = ap.parse_args()
@@ -173,7 +176,9 @@ def main():
     import torch.distributed as dist
     from qw38_b200 import _lib as L
     from qw38_b200 import synth
-    from qw38_b200.q4k_q8 import new_q8_input, pack_q8, q4k_q8_project, set_launch_overlap
+    from qw38_b200.q4k_q8 import (new_q8_input, pack_q8, peer_wait, q4k_q8_project, q4k_q8_project_gather,
+                                  set_launch_overlap)
+    from qw38_b200.sharding import symmetric_pool
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -217,13 +222,39 @@ def main():
             if world > 1:  # rank g's slice lands in gathered[g]; out[t, g*per + j] = gathered[g, t, j]
                 gathered[(m, i)] = torch.empty((world * m, per), dtype=torch.float32, device=dev)
 
+    # Fused gather: every rank's full [m, n] outputs and one arrival-counter array live in one symmetric
+    # allocation, so each projection kernel can store its rows straight into every peer.
+    fused = world > 1 and args.gather == "fused"
+    full, full_ptrs, flag_ptrs = {}, {}, []
+    if fused:
+        try:
+            words = sum(m * n for m in TOKENS for _, n, _ in SHAPES) + 8
+            pool, bases, pool_handle = symmetric_pool(words, dev)
+            off = 0
+            for m in TOKENS:
+                for i, (_, n, _) in enumerate(SHAPES):
+                    full[(m, i)] = pool[off:off + m * n].view(m, n)
+                    full_ptrs[(m, i)] = [b + 4 * off for b in bases]
+                    off += m * n
+            flag_ptrs = [b + 4 * off for b in bases]
+        except Exception as exc:  # symmetric memory can be unavailable; the NCCL path still measures the shards
+            fused = False
+            print(f"[bench] symmetric memory unavailable ({type(exc).__name__}: {exc}); using NCCL all-gather", file=sys.stderr)
+        ok = torch.tensor([1 if fused else 0], device=dev)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+        fused = bool(ok.item())
+
     launches = {"n": 0}
 
-    def projection(m, i, layer, count=True):
+    def projection(m, i, layer, count=True, force_nccl=False):
         _, n, k = SHAPES[i]
-        q4k_q8_project(layers[layer][i], q8[m][k], out=outs[(m, i)], trusted=True)
         if count:
             launches["n"] += 1
+        if fused and not force_nccl:
+            row0, _, _ = shard(n)
+            q4k_q8_project_gather(layers[layer][i], q8[m][k], full_ptrs[(m, i)], flag_ptrs, rank, row0, n)
+            return
+        q4k_q8_project(layers[layer][i], q8[m][k], out=outs[(m, i)], trusted=True)
         if world > 1:
             dist.all_gather_into_tensor(gathered[(m, i)], outs[(m, i)])
 
@@ -245,6 +276,10 @@ def main():
                 if only_kernel and which_kernel(m, layers[layer][i].n) != only_kernel:
                     continue
                 projection(m, i, layer, count)
+        if fused:  # the step's outputs are complete on this rank once every peer has delivered as many projections
+            peer_wait(flag_ptrs[rank], world, rank)
+            if count:
+                launches["n"] += 1
 
     stream = torch.cuda.Stream(device=dev)
 
@@ -281,6 +316,26 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = float(t.item())
         return ms
+
+    if fused:
+        # One untimed step both ways: the fused stores must reproduce the NCCL all-gather bit for bit.
+        for m in TOKENS:
+            for k in (5120, 17408):
+                pack_q8(x_in[m][k], failure, out=q8[m][k])
+            for i in range(len(SHAPES)):
+                projection(m, i, 0, count=False)
+        peer_wait(flag_ptrs[rank], world, rank)
+        torch.cuda.synchronize(dev)
+        dist.barrier()
+        for m in TOKENS:
+            for i, (_, n, _) in enumerate(SHAPES):
+                projection(m, i, 0, count=False, force_nccl=True)
+                _, _, per = shard(n)
+                want = gathered[(m, i)].view(world, m, per).permute(1, 0, 2).reshape(m, world * per)[:, :n]
+                if not torch.equal(full[(m, i)], want):
+                    raise SystemExit(f"fused gather differs from NCCL all-gather at m={m}, matrix {i}")
+        torch.cuda.synchronize(dev)
+        dist.barrier()
 
     # The weights are final from here on, which is what the overlapped launches require.
     torch.cuda.synchronize()
@@ -320,7 +375,7 @@ def main():
     ms = timed(graph, replays)
     t1 = time.time()
     clocks = sampler.stop(t0, t1) if rank == 0 else None
-    launches_per_step = len(TOKENS) * (2 + len(SHAPES))
+    launches_per_step = len(TOKENS) * (2 + len(SHAPES)) + (1 if fused else 0)
     total_bytes = step_bytes()
     value = total_bytes * steps / (ms * 1e-3) / 1e9
     if failure.item() != 0:
@@ -361,15 +416,16 @@ def main():
             per_m[str(m)] = round(b / (mm_ms * 1e-3) / 1e9, 1)
 
     # End to end: host buffers in, host buffers out, copies inside the timed region.
+    result_tensors = full if fused else (gathered if world > 1 else outs)
     h_in = {m: {k: x_in[m][k].cpu().pin_memory() for k in (5120, 17408)} for m in TOKENS}
-    h_out = {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in (gathered if world > 1 else outs).items()}
+    h_out = {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in result_tensors.items()}
 
     def e2e_step(s):
         for m in TOKENS:
             for k in (5120, 17408):
                 x_in[m][k].copy_(h_in[m][k], non_blocking=True)
         one_step(s, count=False)
-        for key, t in (gathered if world > 1 else outs).items():
+        for key, t in result_tensors.items():
             h_out[key].copy_(t, non_blocking=True)
 
     ge = capture(e2e_step, UNROLL) if use_graph else Eager(e2e_step, UNROLL)
@@ -416,7 +472,9 @@ def main():
                 "config": {"workload": "config[1]: decode projection set QKV 7168x5120, O 5120x5120, gate+up 34816x5120, "
                                        "down 5120x17408, Q4_K weights, M in {1,2,4,8,16}, bf16 activations quantised on device",
                            "layers_rotated": LAYERS, "l2": f"weights rotate over {LAYERS} layer copies (1.49 GB) > 126 MB L2",
-                           "parallelism": f"rows/{world}" + (" + NCCL all-gather" if world > 1 else ""),
+                           "parallelism": f"rows/{world}" + ((" + peer stores fused into the projection kernel, one bounded "
+                                                                     "cross-GPU wait per step") if fused else
+                                                                    (" + NCCL all-gather" if world > 1 else "")),
                            "launch": ("CUDA graph replay" if use_graph else "eager") +
                                      ("" if args.no_overlap else ", programmatic dependent launch"),
                            "bytes_per_step": total_bytes},

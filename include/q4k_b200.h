@@ -93,6 +93,31 @@ const char* q4k_last_error(void);   /* thread-local text of the last failure */
 int q4k_last_cuda_status(void);     /* cudaError_t of the last Q4K_ERR_STATUS */
 uint32_t q4k_abi_version(void);
 
+/* Row-sharded decode with the gather fused into the projection (no counterpart in the reference, which is
+ * single-GPU; BASELINE north_star: "N is split across 1/2/4/8 GPUs ... all-gather of the output slices").
+ * Every rank holds a full [m][total_rows] fp32 output buffer and a uint32[8] flag array, both mapped into
+ * every other rank's address space (CUDA IPC, VMM or torch symmetric memory; plain peer stores, no
+ * multicast).  q4k_q8_project_gather runs this rank's weight shard (rows row_offset ..
+ * row_offset + shard->n) and stores each value into ALL ranks' buffers at
+ * [token * total_rows + row_offset + row]; when its last block is done it adds 1 to flags[g][rank] on
+ * every rank g.  `residual`, if given, is [m][total_rows] like the outputs.  m <= 16, shards 16-byte
+ * aligned (a multiple of 8 rows always is).
+ * q4k_peer_wait enqueues a one-warp kernel that waits until every peer's counter in this rank's own flag
+ * array has reached this rank's own counter -- i.e. every rank has delivered as many projections as this
+ * rank has issued -- which is when the gathered outputs of the step may be read.  The wait gives up after
+ * limit_cycles SM clocks (0 = about two seconds) and then sets the status word of q4k_kernel_status.
+ * All ranks must enqueue the same sequence of gather projections. */
+typedef struct q4k_gather_desc {
+  float* outputs[8];    /* outputs[g]: rank g's buffer as addressable from this process */
+  uint32_t* flags[8];   /* flags[g]: rank g's flag array as addressable from this process; start zeroed */
+  uint32_t ranks, rank;
+  uint32_t row_offset;  /* first output row of this rank's shard; a multiple of 8 */
+  uint32_t total_rows;  /* N of the whole matrix */
+} q4k_gather_desc;
+int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gather_desc* desc,
+                          const float* residual, uint64_t residual_len, void* stream);
+int q4k_peer_wait(const uint32_t* flags, uint32_t ranks, uint32_t rank, uint64_t limit_cycles, void* stream);
+
 /* Programmatic dependent launch for the decode path (no counterpart in the reference, which
  * replays its decode step as a CUDA graph of fully serialised kernels, src/runtime/language_model.cpp:324-356).
  * When enabled (process-wide, default off), q4k_pack_q8_*, and q4k_q8_project* for m <= 16 launch
@@ -106,10 +131,11 @@ uint32_t q4k_abi_version(void);
 void q4k_set_launch_overlap(int enabled);
 int q4k_get_launch_overlap(void);
 
-/* Synchronises the current device and reads the status word of the tcgen05 kernel (library-owned
- * scratch): 0 = every launch so far ran to completion; nonzero = a bounded wait inside the
- * kernel gave up at that site and the affected block returned without writing its outputs.
- * No counterpart in the reference, whose kernels have no device-side waits. */
+/* Synchronises the current device and reads the status word shared by the kernels that wait on
+ * device-side barriers (tcgen05, TMA gemv, peer wait; library-owned scratch): 0 = every launch so
+ * far ran to completion; nonzero = a bounded wait gave up at that site (0x5xx TMA gemv, 0x610 peer
+ * wait, others tcgen05) and the affected block returned without writing its outputs.  A nonzero
+ * word is cleared by the read.  No counterpart in the reference, whose kernels have no device-side waits. */
 int q4k_kernel_status(int* value);
 
 /* Padding rules (decode_pad_n / decode_pad_k / decode_code_bytes / decode_scale_bytes,

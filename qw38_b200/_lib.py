@@ -34,6 +34,11 @@ class ProjectOptions(C.Structure):
                 ("workspace_bytes", C.c_uint64), ("flags", C.c_uint32)]
 
 
+class GatherDesc(C.Structure):
+    _fields_ = [("outputs", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("ranks", C.c_uint32), ("rank", C.c_uint32),
+                ("row_offset", C.c_uint32), ("total_rows", C.c_uint32)]
+
+
 _u32, _u64, _vp, _i = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int
 _WP, _OP = C.POINTER(Weight), C.POINTER(ProjectOptions)
 
@@ -57,6 +62,8 @@ SIGNATURES = {
     "q4k_q8_project_ex": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _OP, _vp]),
     "q4k_q8_project_static": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _u32, _vp]),
     "q4k_project_workspace_bytes": (_u64, [_u32, _u32, _u32]),
+    "q4k_q8_project_gather": (_i, [_WP, Q8, C.POINTER(GatherDesc), _vp, _u64, _vp]),
+    "q4k_peer_wait": (_i, [_vp, _u32, _u32, _u64, _vp]),
     "q4k_q8_project_ragged": (_i, [_WP, Q8, C.POINTER(_u32), _u32, _vp, _u64, _OP, _vp]),
     "q4k_repack_blocks144": (_i, [_vp, _u64, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),
     "q4k_q8_mlp_workspace_bytes": (_u64, [_u32, _u32, _u32]),

@@ -350,6 +350,61 @@ int q4k_kernel_status(int* value) {
   if (!p) return Q4K_OK;  // nothing has used the library-owned scratch yet
   Q4K_CUDA(cudaDeviceSynchronize(), "kernel_status.sync");
   Q4K_CUDA(cudaMemcpy(value, static_cast<uint8_t*>(p) + kTicketRegion - 4, 4, cudaMemcpyDeviceToHost), "kernel_status.read");
+  if (*value != 0) Q4K_CUDA(cudaMemset(static_cast<uint8_t*>(p) + kTicketRegion - 4, 0, 4), "kernel_status.clear");
+  return Q4K_OK;
+}
+
+int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gather_desc* desc, const float* residual,
+                          uint64_t residual_len, void* stream_handle) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (int st = valid_weight(shard, "shard")) return st;
+  const q4k_weight& w = *shard;
+  if (!desc) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: null descriptor");
+  if (!valid_input(x) || x.k != w.k) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: invalid geometry");
+  if (desc->ranks < 1 || desc->ranks > 8 || desc->rank >= desc->ranks || desc->row_offset % 8 != 0 ||
+      uint64_t(desc->row_offset) + w.n > desc->total_rows)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: ranks 1..8, rank < ranks, row_offset a multiple of 8 and inside total_rows");
+  for (uint32_t g = 0; g < desc->ranks; ++g)
+    if (!desc->outputs[g] || reinterpret_cast<uintptr_t>(desc->outputs[g]) % 4 != 0 || !desc->flags[g] ||
+        reinterpret_cast<uintptr_t>(desc->flags[g]) % 4 != 0)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: every rank needs a 4-byte aligned output and flag array");
+  if ((residual_len != 0 && residual_len != uint64_t(x.m) * desc->total_rows) || (residual_len != 0 && !residual))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: residual must cover m x total_rows");
+  if (!q4k::gemv_tma_supported(view(w), view(x)))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: needs m <= 16 and 16-byte aligned weight shards");
+  // Peer mappings cannot be checked against this device's allocations; the local operands are.
+  Region regions[5] = {{w.codes, w.codes_bytes, 4, "shard.codes"},
+                       {w.scales, w.scales_bytes, 2, "shard.scales"},
+                       {x.codes, x.codes_len, 4, "input.codes"},
+                       {x.scales, x.scales_len * 4, 4, "input.scales"},
+                       {x.sums, x.sums_len * 4, 4, "input.sums"}};
+  if (int st = check_distinct(regions, 5, false)) return st;
+  q4k::GemvTmaPlan plan = q4k::plan_gemv_tma(x.m, w.n, w.padded_k / 256, 0, 0);
+  uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
+  void* scratch = nullptr;
+  if (int st = own_scratch(partial_bytes, &scratch)) return st;
+  uint8_t* const base = static_cast<uint8_t*>(scratch);
+  q4k::GemvTmaGather gather{};
+  for (uint32_t g = 0; g < desc->ranks; ++g) { gather.outputs[g] = desc->outputs[g]; gather.flags[g] = desc->flags[g]; }
+  gather.done = reinterpret_cast<uint32_t*>(base + kTicketRegion - 8);
+  gather.ranks = desc->ranks; gather.rank = desc->rank; gather.row_offset = desc->row_offset; gather.total_rows = desc->total_rows;
+  Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), nullptr, residual_len ? residual : nullptr, nullptr, plan,
+                                base + kTicketRegion, reinterpret_cast<uint32_t*>(base),
+                                reinterpret_cast<int*>(base + kTicketRegion - 4), stream, &gather),
+           "q4k_q8.gemv_tma_gather");
+  return Q4K_OK;
+}
+
+int q4k_peer_wait(const uint32_t* flags, uint32_t ranks, uint32_t rank, uint64_t limit_cycles, void* stream_handle) {
+  if (!flags || ranks < 1 || ranks > 8 || rank >= ranks)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "peer_wait: flags, ranks 1..8, rank < ranks");
+  void* scratch = nullptr;
+  if (int st = own_scratch(0, &scratch)) return st;
+  long long const limit = limit_cycles ? static_cast<long long>(limit_cycles) : 4000000000LL;
+  Q4K_CUDA(q4k::launch_peer_wait(flags, ranks, rank, limit,
+                                 reinterpret_cast<int*>(static_cast<uint8_t*>(scratch) + kTicketRegion - 4),
+                                 static_cast<cudaStream_t>(stream_handle)),
+           "peer_wait");
   return Q4K_OK;
 }
 

@@ -45,8 +45,12 @@ struct GtParams {
   const int8_t* xcodes;
   const float* xscales;
   const int32_t* xsums;
-  const float* residual;
-  float* out;
+  const float* residual;      // same geometry as the destinations
+  float* out[8];              // destinations: one buffer, or every rank's copy of the gathered output
+  uint32_t* peer_flag[8];     // gather only: rank g's arrival counters (uint32[8]); this launch adds 1 to [rank]
+  uint32_t* done;             // gather only: block counter of this launch, zero on entry and on exit
+  uint32_t ndst, rank;        // number of destinations; this rank
+  uint32_t out_stride, out_row0;  // destination element of (token, row) = token * out_stride + out_row0 + row
   int32_t* partials;  // optional int32 K32 dots [m][n][G]
   float* slices;      // split-K scratch [slice][m][n]
   uint32_t* tickets;  // one per row range, zero on entry and on exit
@@ -175,11 +179,19 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     uint32_t const nt = warp - kFirstReducer;
     uint32_t const r = lane >> 2, q = lane & 3;
     pdl_wait();
-    float* const dst = p.split_k > 1 ? p.slices + size_t(slice) * p.m * p.n : p.out;
-    const float* const res = p.split_k == 1 ? p.residual : nullptr;
+    bool const to_slices = p.split_k > 1;
+    float* const slice_dst = p.slices + size_t(slice) * p.m * p.n;
     uint32_t const tok0 = nt * 8 + q * 2;
     bool const live0 = tok0 < p.m, live1 = tok0 + 1 < p.m;
-    size_t const o0 = size_t(tok0) * p.n, o1 = o0 + p.n;
+    // element offsets of (tok0, row 0) in the K slice's scratch tile and in the destinations
+    size_t const s0 = size_t(tok0) * p.n, s1 = s0 + p.n;
+    size_t const o0 = size_t(tok0) * p.out_stride + p.out_row0, o1 = o0 + p.out_stride;
+    auto put = [&](bool live, size_t so, size_t oo, uint32_t row, float v) {
+      if (!live || row >= p.n) return;
+      if (to_slices) { slice_dst[so + row] = v; return; }
+      if (p.residual) v += p.residual[oo + row];
+      for (uint32_t g = 0; g < p.ndst; ++g) p.out[g][oo + row] = v;
+    };
     for (uint32_t it = 0; it < ntiles; ++it) {
       uint32_t const s = it & slot_mask, use = it >> slot_shift;
       if (!mbar_wait(b_rfull + 8 * s, use & 1, abort_flag, p.status, 0x520)) break;
@@ -194,16 +206,12 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       }
       mbar_arrive(b_rempty + 8 * s);
       uint32_t const row = (t0 + it) * 16 + r;
-      if (row < p.n) {
-        if (live0) dst[o0 + row] = lo.x + (res ? res[o0 + row] : 0.f);
-        if (live1) dst[o1 + row] = lo.y + (res ? res[o1 + row] : 0.f);
-      }
-      if (row + 8 < p.n) {
-        if (live0) dst[o0 + row + 8] = hi.x + (res ? res[o0 + row + 8] : 0.f);
-        if (live1) dst[o1 + row + 8] = hi.y + (res ? res[o1 + row + 8] : 0.f);
-      }
+      put(live0, s0, o0, row, lo.x);
+      put(live1, s1, o1, row, lo.y);
+      put(live0, s0, o0, row + 8, hi.x);
+      put(live1, s1, o1, row + 8, hi.y);
     }
-    __threadfence();
+    if (p.ndst > 1) __threadfence_system(); else __threadfence();
   } else if (warp - kFirstConsumer < nact) {
     uint32_t const w = warp - kFirstConsumer, sb = sb0 + w;
     uint32_t const r = lane >> 2, q = lane & 3;
@@ -385,8 +393,26 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         size_t const o = size_t(tok) * p.n + row;
         float v = __ldcg(p.slices + o);
         for (uint32_t sl = 1; sl < p.split_k; ++sl) v += __ldcg(p.slices + size_t(sl) * p.m * p.n + o);
-        if (p.residual) v += p.residual[o];
-        p.out[o] = v;
+        size_t const oo = size_t(tok) * p.out_stride + p.out_row0 + row;
+        if (p.residual) v += p.residual[oo];
+        for (uint32_t g = 0; g < p.ndst; ++g) p.out[g][oo] = v;
+      }
+      if (p.ndst > 1) __threadfence_system();
+    }
+  }
+
+  // ---- gather: the last block of the grid tells every rank that this rank's rows are in place ----
+  if (p.done != nullptr) {
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      pdl_wait();  // the counter may still belong to the kernel before this one
+      __threadfence_system();
+      uint32_t const old = atomicAdd(p.done, 1u);
+      if (old == gridDim.x - 1) {
+        *p.done = 0;
+        __threadfence_system();
+        if (!*abort_flag)
+          for (uint32_t g = 0; g < p.ndst; ++g) atomicAdd_system(p.peer_flag[g] + p.rank, 1u);
       }
     }
   }
@@ -457,12 +483,15 @@ GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
 }
 
 cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
-                            const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream) {
+                            const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream,
+                            const GemvTmaGather* gather) {
   uint32_t const nt = x.m <= 8 ? 1 : 2;
   uint32_t const cw = plan.warps;
   if (x.m == 0 || x.m > kGemvTmaMaxTokens || cw < 1 || cw > (nt == 1 ? kGemvTmaMaxWarpsNarrow : kGemvTmaMaxWarpsWide) ||
       plan.split_k * cw < w.tiles_k || plan.stages < 2 || plan.stages > uint32_t(kMaxStages) ||
-      (plan.red_slots != 1 && plan.red_slots != 2) || smem_bytes(cw, nt, plan.stages, plan.red_slots) > kSmemBudget || (plan.split_k > 1 && (!slices || !tickets)))
+      (plan.red_slots != 1 && plan.red_slots != 2) || smem_bytes(cw, nt, plan.stages, plan.red_slots) > kSmemBudget ||
+      (plan.split_k > 1 && (!slices || !tickets)) ||
+      (gather && (gather->ranks < 1 || gather->ranks > 8 || gather->rank >= gather->ranks || !gather->done || partials)))
     return cudaErrorInvalidValue;
   CUtensorMap tm_codes, tm_meta;
   uint64_t const rgs = w.padded_n / 8;
@@ -478,9 +507,19 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
     if (!make_map(&tm_meta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.meta, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
       return cudaErrorInvalidValue;
   }
-  GtParams p{x.codes, x.scales, x.sums, residual, out, partials, static_cast<float*>(slices), tickets, status,
-             w.n, x.m, x.padded_k, w.tiles_k, x.padded_k / 32, (w.padded_n + 15) / 16, cw, plan.split_k,
-             plan.tiles_per_range, plan.stages, plan.red_slots};
+  GtParams p{};
+  p.xcodes = x.codes; p.xscales = x.scales; p.xsums = x.sums; p.residual = residual;
+  if (gather) {
+    for (uint32_t g = 0; g < gather->ranks; ++g) { p.out[g] = gather->outputs[g]; p.peer_flag[g] = gather->flags[g]; }
+    p.done = gather->done; p.ndst = gather->ranks; p.rank = gather->rank;
+    p.out_stride = gather->total_rows; p.out_row0 = gather->row_offset;
+  } else {
+    p.out[0] = out; p.done = nullptr; p.ndst = 1; p.rank = 0; p.out_stride = w.n; p.out_row0 = 0;
+  }
+  p.partials = partials; p.slices = static_cast<float*>(slices); p.tickets = tickets; p.status = status;
+  p.n = w.n; p.m = x.m; p.padded_k = x.padded_k; p.tiles_k = w.tiles_k; p.G = x.padded_k / 32;
+  p.row_tiles = (w.padded_n + 15) / 16; p.cw = cw; p.split_k = plan.split_k;
+  p.tiles_per_range = plan.tiles_per_range; p.stages = plan.stages; p.red_slots = plan.red_slots;
   uint32_t const grid = plan.ranges * plan.split_k, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
   bool const dump = partials != nullptr;
   if (nt == 1) {

@@ -82,8 +82,23 @@ struct GemvTmaPlan {
 };
 bool gemv_tma_supported(const WeightView& w, const Q8View& x);
 GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request, uint32_t warps_request);
+// Row-sharded use: every value is stored into each rank's copy of the gathered [m][total_rows] output
+// (peer pointers mapped into this process) and, when the whole grid has finished, this rank's
+// counter is bumped in every rank's flag array.  `done` is a zeroed uint32 the launch returns to zero.
+struct GemvTmaGather {
+  float* outputs[8];
+  uint32_t* flags[8];
+  uint32_t* done;
+  uint32_t ranks, rank, row_offset, total_rows;
+};
 cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
-                            const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream);
+                            const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream,
+                            const GemvTmaGather* gather = nullptr);
+
+// peer.cu : waits (bounded) until every rank's counter in `flags` (uint32[ranks], local memory that
+// peers write) has reached this rank's own; a wait that gives up writes `code` to *status.
+cudaError_t launch_peer_wait(const uint32_t* flags, uint32_t ranks, uint32_t rank, long long limit_cycles, int* status,
+                             cudaStream_t stream);
 
 // abi.cu : process-wide switch set by q4k_set_launch_overlap().  When on, the decode kernels
 // (pack, dp4a, TMA gemv) are launched with programmatic stream serialization: they may start,

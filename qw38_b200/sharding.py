@@ -5,7 +5,7 @@ run of row groups (8 rows, the unit of the split-tile layout), quantises the rep
 activations itself, and the [m, rows] output slices are all-gathered.  No other exchange."""
 from __future__ import annotations
 
-from typing import Tuple
+from typing import List, Tuple
 
 
 def row_shard(n: int, world: int, rank: int) -> Tuple[int, int, int]:
@@ -23,3 +23,43 @@ def gathered_to_token_major(gathered, n: int):
     gathered[g]).  Returns the [m, n] token-major view-or-copy: out[t, g*per + j] = gathered[g, t, j]."""
     world, m, per = gathered.shape
     return gathered.permute(1, 0, 2).reshape(m, world * per)[:, :n]
+
+
+class GatheredOutputs:
+    """Every rank's copy of a gathered [m, n] fp32 output, addressable from this process, plus the
+    per-rank arrival counters, for q4k_q8_project_gather / peer_wait.
+
+    `from_local` builds the single-process form (every "rank" is a tensor of this device), which is how
+    the kernel path is tested on one GPU.  `from_symmetric_memory` allocates the buffers with
+    torch.distributed._symmetric_memory and exchanges the mappings over the default process group."""
+
+    def __init__(self, local_out, local_flags, out_ptrs: List[int], flag_ptrs: List[int], rank: int, keep=None):
+        self.out, self.flags, self.out_ptrs, self.flag_ptrs, self.rank, self._keep = \
+            local_out, local_flags, out_ptrs, flag_ptrs, rank, keep
+
+    @property
+    def world(self) -> int:
+        return len(self.out_ptrs)
+
+    @staticmethod
+    def from_local(outs, flags, rank: int) -> "GatheredOutputs":
+        return GatheredOutputs(outs[rank], flags[rank], [t.data_ptr() for t in outs], [t.data_ptr() for t in flags], rank,
+                               keep=(outs, flags))
+
+
+
+def symmetric_pool(words: int, device, group=None):
+    """A zeroed fp32 buffer of `words` elements allocated on every rank with
+    torch.distributed._symmetric_memory.  Returns (local tensor, [device address of rank g's buffer in
+    this process], handle); keep the handle alive as long as the addresses are used."""
+    import torch
+    import torch.distributed as dist
+    import torch.distributed._symmetric_memory as symm
+
+    group = group or dist.group.WORLD
+    buf = symm.empty(words, dtype=torch.float32, device=device)
+    buf.zero_()
+    handle = symm.rendezvous(buf, group.group_name)
+    torch.cuda.synchronize(device)
+    dist.barrier(group)
+    return buf, [int(handle.buffer_ptrs[g]) for g in range(dist.get_world_size(group))], handle

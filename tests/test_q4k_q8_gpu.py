@@ -396,6 +396,46 @@ def test_launch_overlap_gives_identical_results():
     assert f.item() == 0 and kernel_status() == 0
 
 
+@pytest.mark.parametrize("m,k,world", [(3, 5120, 3), (16, 5120, 2), (8, 17408, 4)])
+def test_project_gather_emulated_ranks(m, k, world):
+    """Row shards whose projection kernel stores into every rank's copy of the output and then bumps the
+    rank's arrival counter.  The ranks are emulated on one GPU: peer buffers are just other tensors, and the
+    launches run one after the other, so nothing ever waits on a kernel that has not run."""
+    from qw38_b200.q4k_q8 import q4k_q8_project_gather, peer_wait
+    from qw38_b200.sharding import row_shard
+    n = 2000
+    w = synth.device_weight(n, k, seed=world)
+    xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=m))
+    q = pack_q8(bf16_tensor(xb), flag())
+    res = dev(synth.activations(m, n, seed=9))
+    full = q4k_q8_project(w, q, residual=res, kernel=L.KERNEL_GEMV_TMA)
+    outs = [torch.full((m, n), -9.0, dtype=torch.float32, device=DEV) for _ in range(world)]
+    flags = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(world)]
+    optr, fptr = [t.data_ptr() for t in outs], [t.data_ptr() for t in flags]
+    for rnd in range(2):                      # counters keep counting across steps
+        for rank in range(world):
+            row0, rows, _ = row_shard(n, world, rank)
+            q4k_q8_project_gather(w.row_slice(row0, rows), q, optr, fptr, rank, row0, n, residual=res)
+        for rank in range(world):
+            peer_wait(fptr[rank], world, rank)
+        torch.cuda.synchronize()
+        for g in range(world):
+            assert flags[g][:world].tolist() == [rnd + 1] * world
+            err = (outs[g] - full).abs().max().item()
+            assert err <= 1e-4 * full.abs().max().item(), f"rank {g}: {err}"
+            outs[g].fill_(-9.0)
+    assert kernel_status() == 0
+    # A peer that never delivers: the wait runs out after ~1 ms of SM clocks and reports it; the context stays usable.
+    flags[0][1] -= 1
+    peer_wait(fptr[0], world, 0, limit_cycles=2_000_000)
+    assert kernel_status() == 0x610
+    assert kernel_status() == 0, "the read clears the word"
+    with pytest.raises(Q4KError):
+        q4k_q8_project_gather(w.row_slice(0, 1000), q, optr, fptr, world, 0, n)          # rank outside the world
+    with pytest.raises(Q4KError):
+        q4k_q8_project_gather(w.row_slice(1000, 1000), q, optr, fptr, 0, 1004, n)        # shard would overrun total_rows
+
+
 def ragged_offsets():
     lens = [1] * 48 + [512, 237, 1024]
     return np.concatenate([[0], np.cumsum(lens)]).astype(np.uint32)
