@@ -228,7 +228,7 @@ def main():
     full, full_ptrs, flag_ptrs = {}, {}, []
     if fused:
         try:
-            words = sum(m * n for m in TOKENS for _, n, _ in SHAPES) + 8
+            words = sum(m * n for m in TOKENS for _, n, _ in SHAPES) + 16
             pool, bases, pool_handle = symmetric_pool(words, dev)
             off = 0
             for m in TOKENS:
@@ -254,7 +254,9 @@ def main():
             row0, _, _ = shard(n)
             q4k_q8_project_gather(layers[layer][i], q8[m][k], full_ptrs[(m, i)], flag_ptrs, rank, row0, n)
             return
-        q4k_q8_project(layers[layer][i], q8[m][k], out=outs[(m, i)], trusted=True)
+        # the check of the fused path pins the kernel: automatic choice for one token depends on the overlap switch
+        q4k_q8_project(layers[layer][i], q8[m][k], out=outs[(m, i)], trusted=True,
+                       kernel=L.KERNEL_GEMV_TMA if force_nccl else L.KERNEL_AUTO)
         if world > 1:
             dist.all_gather_into_tensor(gathered[(m, i)], outs[(m, i)])
 
@@ -277,7 +279,7 @@ def main():
                     continue
                 projection(m, i, layer, count)
         if fused:  # the step's outputs are complete on this rank once every peer has delivered as many projections
-            peer_wait(flag_ptrs[rank], world, rank)
+            peer_wait(flag_ptrs, rank)
             if count:
                 launches["n"] += 1
 
@@ -324,7 +326,7 @@ def main():
                 pack_q8(x_in[m][k], failure, out=q8[m][k])
             for i in range(len(SHAPES)):
                 projection(m, i, 0, count=False)
-        peer_wait(flag_ptrs[rank], world, rank)
+        peer_wait(flag_ptrs, rank)
         torch.cuda.synchronize(dev)
         dist.barrier()
         for m in TOKENS:

@@ -95,28 +95,34 @@ uint32_t q4k_abi_version(void);
 
 /* Row-sharded decode with the gather fused into the projection (no counterpart in the reference, which is
  * single-GPU; BASELINE north_star: "N is split across 1/2/4/8 GPUs ... all-gather of the output slices").
- * Every rank holds a full [m][total_rows] fp32 output buffer and a uint32[8] flag array, both mapped into
+ * Every rank holds a full [m][total_rows] fp32 output buffer and a zeroed uint32[16] flag array (words 0-7:
+ * deliveries per rank; 8-9: this rank's own bookkeeping), both mapped into
  * every other rank's address space (CUDA IPC, VMM or torch symmetric memory; plain peer stores, no
  * multicast).  q4k_q8_project_gather runs this rank's weight shard (rows row_offset ..
  * row_offset + shard->n) and stores each value into ALL ranks' buffers at
- * [token * total_rows + row_offset + row]; when its last block is done it adds 1 to flags[g][rank] on
- * every rank g.  `residual`, if given, is [m][total_rows] like the outputs.  m <= 16, shards 16-byte
- * aligned (a multiple of 8 rows always is).
- * q4k_peer_wait enqueues a one-warp kernel that waits until every peer's counter in this rank's own flag
- * array has reached this rank's own counter -- i.e. every rank has delivered as many projections as this
- * rank has issued -- which is when the gathered outputs of the step may be read.  The wait gives up after
- * limit_cycles SM clocks (0 = about two seconds) and then sets the status word of q4k_kernel_status.
- * All ranks must enqueue the same sequence of gather projections. */
+ * [token * total_rows + row_offset + row] with plain peer stores, and counts itself as finished.  Finished
+ * projections are announced -- flags[g][rank] += count on every rank g -- by the next gather projection or
+ * peer wait of the same stream, i.e. once the grid has completed and its stores are visible system-wide
+ * (no system-scope fence inside the hot kernel).  `residual`, if given, is [m][total_rows] like the
+ * outputs.  m <= 16, shards 16-byte aligned (a multiple of 8 rows always is).
+ * q4k_peer_wait enqueues a one-warp kernel that announces what is still unannounced and then waits until
+ * every peer's counter in this rank's own flag array has reached this rank's own -- every rank has
+ * delivered as many projections as this rank has issued -- which is when the gathered outputs of the step
+ * may be read.  `outputs` and `row_offset`/`total_rows` of the descriptor are not used by the wait.  The
+ * wait gives up after limit_cycles SM clocks (0 = about two seconds) and then sets the status word of
+ * q4k_kernel_status.  q4k_peer_announce does the announcement alone (a rank that has other work to enqueue
+ * before it needs the peers' rows).  All ranks must enqueue the same sequence of gather projections. */
 typedef struct q4k_gather_desc {
   float* outputs[8];    /* outputs[g]: rank g's buffer as addressable from this process */
-  uint32_t* flags[8];   /* flags[g]: rank g's flag array as addressable from this process; start zeroed */
+  uint32_t* flags[8];   /* flags[g]: rank g's uint32[16] flag array as addressable from this process; start zeroed */
   uint32_t ranks, rank;
   uint32_t row_offset;  /* first output row of this rank's shard; a multiple of 8 */
   uint32_t total_rows;  /* N of the whole matrix */
 } q4k_gather_desc;
 int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gather_desc* desc,
                           const float* residual, uint64_t residual_len, void* stream);
-int q4k_peer_wait(const uint32_t* flags, uint32_t ranks, uint32_t rank, uint64_t limit_cycles, void* stream);
+int q4k_peer_wait(const q4k_gather_desc* desc, uint64_t limit_cycles, void* stream);
+int q4k_peer_announce(const q4k_gather_desc* desc, void* stream);
 
 /* Programmatic dependent launch for the decode path (no counterpart in the reference, which
  * replays its decode step as a CUDA graph of fully serialised kernels, src/runtime/language_model.cpp:324-356).

@@ -63,7 +63,8 @@ SIGNATURES = {
     "q4k_q8_project_static": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _u32, _vp]),
     "q4k_project_workspace_bytes": (_u64, [_u32, _u32, _u32]),
     "q4k_q8_project_gather": (_i, [_WP, Q8, C.POINTER(GatherDesc), _vp, _u64, _vp]),
-    "q4k_peer_wait": (_i, [_vp, _u32, _u32, _u64, _vp]),
+    "q4k_peer_wait": (_i, [C.POINTER(GatherDesc), _u64, _vp]),
+    "q4k_peer_announce": (_i, [C.POINTER(GatherDesc), _vp]),
     "q4k_q8_project_ragged": (_i, [_WP, Q8, C.POINTER(_u32), _u32, _vp, _u64, _OP, _vp]),
     "q4k_repack_blocks144": (_i, [_vp, _u64, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),
     "q4k_q8_mlp_workspace_bytes": (_u64, [_u32, _u32, _u32]),

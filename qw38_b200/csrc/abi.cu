@@ -386,7 +386,9 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
   uint8_t* const base = static_cast<uint8_t*>(scratch);
   q4k::GemvTmaGather gather{};
   for (uint32_t g = 0; g < desc->ranks; ++g) { gather.outputs[g] = desc->outputs[g]; gather.flags[g] = desc->flags[g]; }
-  gather.done = reinterpret_cast<uint32_t*>(base + kTicketRegion - 8);
+  // words 8 and 9 of this rank's own flag array: its unannounced projections and the block counter
+  gather.unsignalled = desc->flags[desc->rank] + 8;
+  gather.done = desc->flags[desc->rank] + 9;
   gather.ranks = desc->ranks; gather.rank = desc->rank; gather.row_offset = desc->row_offset; gather.total_rows = desc->total_rows;
   Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), nullptr, residual_len ? residual : nullptr, nullptr, plan,
                                 base + kTicketRegion, reinterpret_cast<uint32_t*>(base),
@@ -395,18 +397,28 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
   return Q4K_OK;
 }
 
-int q4k_peer_wait(const uint32_t* flags, uint32_t ranks, uint32_t rank, uint64_t limit_cycles, void* stream_handle) {
-  if (!flags || ranks < 1 || ranks > 8 || rank >= ranks)
-    return fail(Q4K_ERR_INVALID_ARGUMENT, "peer_wait: flags, ranks 1..8, rank < ranks");
+static int peer_wait_impl(const q4k_gather_desc* desc, long long limit, void* stream_handle) {
+  if (!desc || desc->ranks < 1 || desc->ranks > 8 || desc->rank >= desc->ranks)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "peer_wait: descriptor with ranks 1..8 and rank < ranks");
+  for (uint32_t g = 0; g < desc->ranks; ++g)
+    if (!desc->flags[g] || reinterpret_cast<uintptr_t>(desc->flags[g]) % 4 != 0)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "peer_wait: every rank needs a 4-byte aligned flag array");
   void* scratch = nullptr;
   if (int st = own_scratch(0, &scratch)) return st;
-  long long const limit = limit_cycles ? static_cast<long long>(limit_cycles) : 4000000000LL;
-  Q4K_CUDA(q4k::launch_peer_wait(flags, ranks, rank, limit,
-                                 reinterpret_cast<int*>(static_cast<uint8_t*>(scratch) + kTicketRegion - 4),
-                                 static_cast<cudaStream_t>(stream_handle)),
+  uint8_t* const base = static_cast<uint8_t*>(scratch);
+  Q4K_CUDA(q4k::launch_peer_wait(desc->flags, desc->flags[desc->rank] + 8, desc->ranks, desc->rank, limit,
+                                 reinterpret_cast<int*>(base + kTicketRegion - 4), static_cast<cudaStream_t>(stream_handle)),
            "peer_wait");
   return Q4K_OK;
 }
+
+int q4k_peer_wait(const q4k_gather_desc* desc, uint64_t limit_cycles, void* stream_handle) {
+  long long const limit = limit_cycles == 0 || limit_cycles > 0x7fffffffffffffffull ? 4000000000LL
+                                                                                    : static_cast<long long>(limit_cycles);
+  return peer_wait_impl(desc, limit, stream_handle);
+}
+
+int q4k_peer_announce(const q4k_gather_desc* desc, void* stream_handle) { return peer_wait_impl(desc, -1, stream_handle); }
 
 int q4k_validate_device_span(const void* pointer, uint64_t bytes, uint32_t alignment, int device) {
   return check_span(Region{pointer, bytes, alignment, "span"}, device);

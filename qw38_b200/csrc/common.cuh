@@ -69,4 +69,15 @@ __device__ __forceinline__ uint32_t odd_bytes(uint32_t z0, uint32_t z1) { return
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
+// Row-sharded decode: tell every rank how many more projections of this rank are complete.  Called by
+// one thread at the start of the kernel that FOLLOWS them in the stream, after pdl_wait(): those grids
+// have completed, so their stores into the peers' buffers are visible before the counters move.
+__device__ __forceinline__ void announce_deliveries(uint32_t* unsignalled, uint32_t* const* peer_flag, uint32_t ranks,
+                                                    uint32_t rank) {
+  uint32_t const u = *reinterpret_cast<volatile uint32_t*>(unsignalled);
+  if (u == 0) return;
+  *reinterpret_cast<volatile uint32_t*>(unsignalled) = 0;
+  for (uint32_t g = 0; g < ranks; ++g) atomicAdd_system(peer_flag[g] + rank, u);
+}
+
 }  // namespace q4k

@@ -47,8 +47,9 @@ struct GtParams {
   const int32_t* xsums;
   const float* residual;      // same geometry as the destinations
   float* out[8];              // destinations: one buffer, or every rank's copy of the gathered output
-  uint32_t* peer_flag[8];     // gather only: rank g's arrival counters (uint32[8]); this launch adds 1 to [rank]
+  uint32_t* peer_flag[8];     // gather only: rank g's arrival counters (uint32[8]); [rank] counts this rank's deliveries
   uint32_t* done;             // gather only: block counter of this launch, zero on entry and on exit
+  uint32_t* unsignalled;      // gather only: finished projections of this rank not yet announced to the peers
   uint32_t ndst, rank;        // number of destinations; this rank
   uint32_t out_stride, out_row0;  // destination element of (token, row) = token * out_stride + out_row0 + row
   int32_t* partials;  // optional int32 K32 dots [m][n][G]
@@ -179,6 +180,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     uint32_t const nt = warp - kFirstReducer;
     uint32_t const r = lane >> 2, q = lane & 3;
     pdl_wait();
+    if (p.done != nullptr && blockIdx.x == 0 && warp == kFirstReducer && lane == 0) announce_deliveries(p.unsignalled, p.peer_flag, p.ndst, p.rank);
     bool const to_slices = p.split_k > 1;
     float* const slice_dst = p.slices + size_t(slice) * p.m * p.n;
     uint32_t const tok0 = nt * 8 + q * 2;
@@ -211,7 +213,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       put(live0, s0, o0, row + 8, hi.x);
       put(live1, s1, o1, row + 8, hi.y);
     }
-    if (p.ndst > 1) __threadfence_system(); else __threadfence();
+    __threadfence();
   } else if (warp - kFirstConsumer < nact) {
     uint32_t const w = warp - kFirstConsumer, sb = sb0 + w;
     uint32_t const r = lane >> 2, q = lane & 3;
@@ -397,22 +399,21 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         if (p.residual) v += p.residual[oo];
         for (uint32_t g = 0; g < p.ndst; ++g) p.out[g][oo] = v;
       }
-      if (p.ndst > 1) __threadfence_system();
     }
   }
 
-  // ---- gather: the last block of the grid tells every rank that this rank's rows are in place ----
+  // ---- gather: the last block of the grid records one more finished projection.  It is announced to
+  // the peers by the next kernel of this stream (announce_deliveries), i.e. after this grid has
+  // completed and its peer stores are visible system-wide, so no system-scope fence is needed here.
   if (p.done != nullptr) {
     __syncthreads();
     if (threadIdx.x == 0) {
-      pdl_wait();  // the counter may still belong to the kernel before this one
-      __threadfence_system();
+      pdl_wait();  // the counters may still belong to the kernel before this one
+      __threadfence();
       uint32_t const old = atomicAdd(p.done, 1u);
       if (old == gridDim.x - 1) {
         *p.done = 0;
-        __threadfence_system();
-        if (!*abort_flag)
-          for (uint32_t g = 0; g < p.ndst; ++g) atomicAdd_system(p.peer_flag[g] + p.rank, 1u);
+        if (!*abort_flag) atomicAdd(p.unsignalled, 1u);
       }
     }
   }
@@ -491,7 +492,7 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
       plan.split_k * cw < w.tiles_k || plan.stages < 2 || plan.stages > uint32_t(kMaxStages) ||
       (plan.red_slots != 1 && plan.red_slots != 2) || smem_bytes(cw, nt, plan.stages, plan.red_slots) > kSmemBudget ||
       (plan.split_k > 1 && (!slices || !tickets)) ||
-      (gather && (gather->ranks < 1 || gather->ranks > 8 || gather->rank >= gather->ranks || !gather->done || partials)))
+      (gather && (gather->ranks < 1 || gather->ranks > 8 || gather->rank >= gather->ranks || !gather->done || !gather->unsignalled || partials)))
     return cudaErrorInvalidValue;
   CUtensorMap tm_codes, tm_meta;
   uint64_t const rgs = w.padded_n / 8;
@@ -511,7 +512,7 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
   p.xcodes = x.codes; p.xscales = x.scales; p.xsums = x.sums; p.residual = residual;
   if (gather) {
     for (uint32_t g = 0; g < gather->ranks; ++g) { p.out[g] = gather->outputs[g]; p.peer_flag[g] = gather->flags[g]; }
-    p.done = gather->done; p.ndst = gather->ranks; p.rank = gather->rank;
+    p.done = gather->done; p.unsignalled = gather->unsignalled; p.ndst = gather->ranks; p.rank = gather->rank;
     p.out_stride = gather->total_rows; p.out_row0 = gather->row_offset;
   } else {
     p.out[0] = out; p.done = nullptr; p.ndst = 1; p.rank = 0; p.out_stride = w.n; p.out_row0 = 0;

@@ -88,17 +88,19 @@ GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
 struct GemvTmaGather {
   float* outputs[8];
   uint32_t* flags[8];
-  uint32_t* done;
+  uint32_t* done;         // zeroed uint32 the launch returns to zero
+  uint32_t* unsignalled;  // finished-but-unannounced projections of this rank (shared with peer wait)
   uint32_t ranks, rank, row_offset, total_rows;
 };
 cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
                             const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream,
                             const GemvTmaGather* gather = nullptr);
 
-// peer.cu : waits (bounded) until every rank's counter in `flags` (uint32[ranks], local memory that
-// peers write) has reached this rank's own; a wait that gives up writes `code` to *status.
-cudaError_t launch_peer_wait(const uint32_t* flags, uint32_t ranks, uint32_t rank, long long limit_cycles, int* status,
-                             cudaStream_t stream);
+// peer.cu : announces this rank's finished projections to every rank, then waits (bounded) until every
+// rank's counter in this rank's own flag array has reached this rank's own; a wait that gives up
+// writes 0x610 to *status.  limit_cycles < 0 announces only.
+cudaError_t launch_peer_wait(uint32_t* const* flags, uint32_t* unsignalled, uint32_t ranks, uint32_t rank,
+                             long long limit_cycles, int* status, cudaStream_t stream);
 
 // abi.cu : process-wide switch set by q4k_set_launch_overlap().  When on, the decode kernels
 // (pack, dp4a, TMA gemv) are launched with programmatic stream serialization: they may start,

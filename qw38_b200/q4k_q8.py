@@ -200,7 +200,7 @@ def q4k_q8_project_ragged(weight: PrefillWeight, x: Q8Input, row_offsets: Sequen
 def q4k_q8_project_gather(shard: PrefillWeight, x: Q8Input, outputs: Sequence[int], flags: Sequence[int], rank: int,
                           row_offset: int, total_rows: int, residual: Optional[torch.Tensor] = None, stream=None) -> None:
     """Row-sharded decode projection with the gather fused in (q4k_q8_project_gather): `outputs[g]` /
-    `flags[g]` are rank g's full [m, total_rows] fp32 buffer and uint32[8] flag array as device addresses
+    `flags[g]` are rank g's full [m, total_rows] fp32 buffer and zeroed uint32[16] flag array as device addresses
     valid in this process.  This rank's rows land in every buffer; flags[g][rank] is then incremented."""
     desc = L.GatherDesc()
     for g, (o, f) in enumerate(zip(outputs, flags)):
@@ -211,9 +211,23 @@ def q4k_q8_project_gather(shard: PrefillWeight, x: Q8Input, outputs: Sequence[in
                                           0 if residual is None else residual.numel(), _stream(stream)))
 
 
-def peer_wait(flags: int, ranks: int, rank: int, limit_cycles: int = 0, stream=None) -> None:
-    """Enqueue the bounded wait for every rank's deliveries (q4k_peer_wait); `flags` is this rank's own array."""
-    _check(L.load().q4k_peer_wait(C.c_void_p(int(flags)), ranks, rank, limit_cycles, _stream(stream)))
+def peer_announce(flags: Sequence[int], rank: int, stream=None) -> None:
+    """Enqueue only the announcement of this rank's finished gather projections (q4k_peer_announce)."""
+    desc = L.GatherDesc()
+    for g, f in enumerate(flags):
+        desc.flags[g] = int(f)
+    desc.ranks, desc.rank = len(flags), rank
+    _check(L.load().q4k_peer_announce(C.byref(desc), _stream(stream)))
+
+
+def peer_wait(flags: Sequence[int], rank: int, limit_cycles: int = 0, stream=None) -> None:
+    """Enqueue the announcement of this rank's finished gather projections and the bounded wait for every
+    rank's deliveries (q4k_peer_wait); `flags[g]` as for q4k_q8_project_gather."""
+    desc = L.GatherDesc()
+    for g, f in enumerate(flags):
+        desc.flags[g] = int(f)
+    desc.ranks, desc.rank = len(flags), rank
+    _check(L.load().q4k_peer_wait(C.byref(desc), limit_cycles, _stream(stream)))
 
 
 def q8_mlp_workspace_bytes(m: int, hidden: int, ffn: int) -> int:

@@ -25,29 +25,6 @@ def gathered_to_token_major(gathered, n: int):
     return gathered.permute(1, 0, 2).reshape(m, world * per)[:, :n]
 
 
-class GatheredOutputs:
-    """Every rank's copy of a gathered [m, n] fp32 output, addressable from this process, plus the
-    per-rank arrival counters, for q4k_q8_project_gather / peer_wait.
-
-    `from_local` builds the single-process form (every "rank" is a tensor of this device), which is how
-    the kernel path is tested on one GPU.  `from_symmetric_memory` allocates the buffers with
-    torch.distributed._symmetric_memory and exchanges the mappings over the default process group."""
-
-    def __init__(self, local_out, local_flags, out_ptrs: List[int], flag_ptrs: List[int], rank: int, keep=None):
-        self.out, self.flags, self.out_ptrs, self.flag_ptrs, self.rank, self._keep = \
-            local_out, local_flags, out_ptrs, flag_ptrs, rank, keep
-
-    @property
-    def world(self) -> int:
-        return len(self.out_ptrs)
-
-    @staticmethod
-    def from_local(outs, flags, rank: int) -> "GatheredOutputs":
-        return GatheredOutputs(outs[rank], flags[rank], [t.data_ptr() for t in outs], [t.data_ptr() for t in flags], rank,
-                               keep=(outs, flags))
-
-
-
 def symmetric_pool(words: int, device, group=None):
     """A zeroed fp32 buffer of `words` elements allocated on every rank with
     torch.distributed._symmetric_memory.  Returns (local tensor, [device address of rank g's buffer in

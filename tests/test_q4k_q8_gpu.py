@@ -401,7 +401,7 @@ def test_project_gather_emulated_ranks(m, k, world):
     """Row shards whose projection kernel stores into every rank's copy of the output and then bumps the
     rank's arrival counter.  The ranks are emulated on one GPU: peer buffers are just other tensors, and the
     launches run one after the other, so nothing ever waits on a kernel that has not run."""
-    from qw38_b200.q4k_q8 import q4k_q8_project_gather, peer_wait
+    from qw38_b200.q4k_q8 import q4k_q8_project_gather, peer_announce, peer_wait
     from qw38_b200.sharding import row_shard
     n = 2000
     w = synth.device_weight(n, k, seed=world)
@@ -410,14 +410,16 @@ def test_project_gather_emulated_ranks(m, k, world):
     res = dev(synth.activations(m, n, seed=9))
     full = q4k_q8_project(w, q, residual=res, kernel=L.KERNEL_GEMV_TMA)
     outs = [torch.full((m, n), -9.0, dtype=torch.float32, device=DEV) for _ in range(world)]
-    flags = [torch.zeros(8, dtype=torch.int32, device=DEV) for _ in range(world)]
+    flags = [torch.zeros(16, dtype=torch.int32, device=DEV) for _ in range(world)]
     optr, fptr = [t.data_ptr() for t in outs], [t.data_ptr() for t in flags]
     for rnd in range(2):                      # counters keep counting across steps
         for rank in range(world):
             row0, rows, _ = row_shard(n, world, rank)
             q4k_q8_project_gather(w.row_slice(row0, rows), q, optr, fptr, rank, row0, n, residual=res)
+        for rank in range(world):         # one stream plays every rank: all announce before anyone waits
+            peer_announce(fptr, rank)
         for rank in range(world):
-            peer_wait(fptr[rank], world, rank)
+            peer_wait(fptr, rank)
         torch.cuda.synchronize()
         for g in range(world):
             assert flags[g][:world].tolist() == [rnd + 1] * world
@@ -427,7 +429,7 @@ def test_project_gather_emulated_ranks(m, k, world):
     assert kernel_status() == 0
     # A peer that never delivers: the wait runs out after ~1 ms of SM clocks and reports it; the context stays usable.
     flags[0][1] -= 1
-    peer_wait(fptr[0], world, 0, limit_cycles=2_000_000)
+    peer_wait(fptr, 0, limit_cycles=2_000_000)
     assert kernel_status() == 0x610
     assert kernel_status() == 0, "the read clears the word"
     with pytest.raises(Q4KError):
