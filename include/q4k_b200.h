@@ -93,6 +93,55 @@ const char* q4k_last_error(void);   /* thread-local text of the last failure */
 int q4k_last_cuda_status(void);     /* cudaError_t of the last Q4K_ERR_STATUS */
 uint32_t q4k_abi_version(void);
 
+/* Decode projection behind launch_decode_mmv / _paired / _ranges (cuda/decode_mmv.hpp:207-215) with a
+ * Q8-K32 activation policy (the reference's enum has only Bf16 = 1, cuda/decode_mmv.hpp:43; this is the
+ * value a maintainer adds): 1..16 bf16 input rows [m][k] are quantised and multiplied in one call, and one of
+ * the reference's four DecodeEpilogue forms (cuda/decode_mmv.hpp:45-51) is applied.  Outputs are [m][n],
+ * token-major.  Validation follows cuda/decode_mmv.cu:440-540: a store epilogue must not supply a residual;
+ * ResidualAddFp32 reads `residual` and writes `output`, or updates `residual` in place when `output` is NULL;
+ * SwigluStoreBf16 needs the paired call, whose B side declares no output and shares A's input.
+ * The Bf16 policy (bf16-rounded weights x bf16 activations, cuda/decode_mmv.cu:121-250) is not built. */
+#define Q4K_EPILOGUE_STORE_BF16 1
+#define Q4K_EPILOGUE_STORE_FP32 2
+#define Q4K_EPILOGUE_RESIDUAL_ADD_FP32 3
+#define Q4K_EPILOGUE_SWIGLU_STORE_BF16 4 /* paired gate/up only: y = bf16(SiLU(a.x) * b.x) */
+#define Q4K_ACTIVATION_BF16 1            /* reference policy; rejected here */
+#define Q4K_ACTIVATION_Q8_K32 2          /* Q8 activations, exact int32 K32 dots */
+
+typedef struct q4k_decode_desc {
+  q4k_weight weight;      /* DecodeMmvDesc layout/quantizer/n/k/padded_*, codes, scales */
+  const uint16_t* input;  /* bf16 [m][k] */
+  uint64_t input_len;     /* m * k */
+  void* output;           /* bf16 or fp32 [m][n] by epilogue; NULL = in-place residual update */
+  uint64_t output_len;    /* m * n elements, 0 when output is NULL */
+  const float* residual;  /* fp32 [m][n] for RESIDUAL_ADD_FP32, else NULL */
+  uint64_t residual_len;
+  uint32_t m;             /* 1..16 (the reference's entry points take one row) */
+  uint8_t epilogue;
+  uint8_t activation_policy;
+} q4k_decode_desc;
+
+/* Scratch for one call: the Q8 pack of the input rows plus fp32 rows for the bf16/SwiGLU epilogues;
+ * n_total = rows of all matrices in the call.  256-byte aligned device memory, caller-owned. */
+uint64_t q4k_decode_workspace_bytes(uint32_t m, uint64_t n_total, uint32_t k);
+int q4k_decode_mmv(const q4k_decode_desc* desc, void* workspace, uint64_t workspace_bytes, int* failure, void* stream);
+int q4k_decode_mmv_paired(const q4k_decode_desc* a, const q4k_decode_desc* b, void* workspace,
+                          uint64_t workspace_bytes, int* failure, void* stream);
+/* Two or three output ranges that share K and input (launch_decode_mmv_ranges): quantised once. */
+int q4k_decode_mmv_ranges(const q4k_decode_desc* ranges, uint32_t count, void* workspace,
+                          uint64_t workspace_bytes, int* failure, void* stream);
+
+/* PrefillEngine::project and ::paired_swiglu (cuda/prefill.hpp:88-96) for Q4_K weights with the quantise ->
+ * MMQ dispatch (a new PrefillDispatch value on the reference side): the descriptor is PrefillProjection
+ * (weight, bf16 input [valid_tokens][k], output, residual, valid_tokens = m, epilogue = PrefillEpilogue
+ * 1..3, same numbering as DecodeEpilogue); first_position is not needed, the arithmetic is position free.
+ * Up to Q4K_MAX_TOKENS rows; workspace as q4k_decode_workspace_bytes(valid_tokens, n, k).
+ * PrefillEngine::mlp is q4k_q8_mlp. */
+int q4k_prefill_project(const q4k_decode_desc* projection, void* workspace, uint64_t workspace_bytes, int* failure,
+                        void* stream);
+int q4k_prefill_paired_swiglu(const q4k_weight* gate, const q4k_weight* up, const uint16_t* normalized, uint16_t* swiglu,
+                              uint32_t valid_tokens, void* workspace, uint64_t workspace_bytes, int* failure, void* stream);
+
 /* Row-sharded decode with the gather fused into the projection (no counterpart in the reference, which is
  * single-GPU; BASELINE north_star: "N is split across 1/2/4/8 GPUs ... all-gather of the output slices").
  * Every rank holds a full [m][total_rows] fp32 output buffer and a zeroed uint32[16] flag array (words 0-7:

@@ -34,6 +34,16 @@ class ProjectOptions(C.Structure):
                 ("workspace_bytes", C.c_uint64), ("flags", C.c_uint32)]
 
 
+class DecodeDesc(C.Structure):
+    _fields_ = [("weight", Weight), ("input", C.c_void_p), ("input_len", C.c_uint64), ("output", C.c_void_p),
+                ("output_len", C.c_uint64), ("residual", C.c_void_p), ("residual_len", C.c_uint64), ("m", C.c_uint32),
+                ("epilogue", C.c_uint8), ("activation_policy", C.c_uint8)]
+
+
+EPILOGUE_STORE_BF16, EPILOGUE_STORE_FP32, EPILOGUE_RESIDUAL_ADD_FP32, EPILOGUE_SWIGLU_STORE_BF16 = 1, 2, 3, 4
+ACTIVATION_BF16, ACTIVATION_Q8_K32 = 1, 2
+
+
 class GatherDesc(C.Structure):
     _fields_ = [("outputs", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("ranks", C.c_uint32), ("rank", C.c_uint32),
                 ("row_offset", C.c_uint32), ("total_rows", C.c_uint32)]
@@ -62,6 +72,12 @@ SIGNATURES = {
     "q4k_q8_project_ex": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _OP, _vp]),
     "q4k_q8_project_static": (_i, [_WP, Q8, _vp, _u64, _vp, _u64, _u32, _vp]),
     "q4k_project_workspace_bytes": (_u64, [_u32, _u32, _u32]),
+    "q4k_decode_workspace_bytes": (_u64, [_u32, _u64, _u32]),
+    "q4k_decode_mmv": (_i, [C.POINTER(DecodeDesc), _vp, _u64, _vp, _vp]),
+    "q4k_decode_mmv_paired": (_i, [C.POINTER(DecodeDesc), C.POINTER(DecodeDesc), _vp, _u64, _vp, _vp]),
+    "q4k_decode_mmv_ranges": (_i, [C.POINTER(DecodeDesc), _u32, _vp, _u64, _vp, _vp]),
+    "q4k_prefill_project": (_i, [C.POINTER(DecodeDesc), _vp, _u64, _vp, _vp]),
+    "q4k_prefill_paired_swiglu": (_i, [_WP, _WP, _vp, _vp, _u32, _vp, _u64, _vp, _vp]),
     "q4k_q8_project_gather": (_i, [_WP, Q8, C.POINTER(GatherDesc), _vp, _u64, _vp]),
     "q4k_peer_wait": (_i, [C.POINTER(GatherDesc), _u64, _vp]),
     "q4k_peer_announce": (_i, [C.POINTER(GatherDesc), _vp]),

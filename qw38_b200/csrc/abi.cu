@@ -164,7 +164,7 @@ constexpr uint32_t kFlagTrustedSpans = 1u;
 
 int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output, uint64_t output_len,
                  const float* residual, uint64_t residual_len, const q4k_project_options* opt,
-                 cudaStream_t stream) {
+                 cudaStream_t stream, bool residual_in_place = false) {
   if (int st = valid_weight(weight, "weight")) return st;
   const q4k_weight& w = *weight;
   if (!valid_input(x) || x.k != w.k || output_len != uint64_t(x.m) * w.n ||
@@ -184,7 +184,8 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
                        {nullptr, 0, 4, ""},
                        {nullptr, 0, 4, ""}};
   int count = 6;
-  if (residual_len) regions[count++] = {residual, residual_len * 4, 4, "residual"};
+  // in place: every kernel reads residual[i] and writes output[i] from the same thread, in that order
+  if (residual_len && !(residual_in_place && residual == output)) regions[count++] = {residual, residual_len * 4, 4, "residual"};
   if (partials) regions[count++] = {partials, opt->partials_len * 4, 4, "partials"};
   if (int st = check_distinct(regions, count, trusted)) return st;
 
@@ -419,6 +420,196 @@ int q4k_peer_wait(const q4k_gather_desc* desc, uint64_t limit_cycles, void* stre
 }
 
 int q4k_peer_announce(const q4k_gather_desc* desc, void* stream_handle) { return peer_wait_impl(desc, -1, stream_handle); }
+
+// ---- decode entry points: quantise bf16 rows, project, apply a DecodeEpilogue -------------------
+namespace {
+uint64_t align256(uint64_t v) { return (v + 255) / 256 * 256; }
+
+struct DecodeScratch {
+  q4k_q8_input q8;
+  float* rows;        // 2 * m * n_total floats
+  uint64_t rows_len;
+};
+
+uint64_t decode_scratch_bytes(uint32_t m, uint64_t n_total, uint32_t k) {
+  uint64_t const pk = (uint64_t(k) + 255) / 256 * 256, G = pk / 32;
+  return align256(uint64_t(m) * pk) + 2 * align256(uint64_t(m) * G * 4) + align256(2 * uint64_t(m) * n_total * 4);
+}
+
+int carve_decode_scratch(void* workspace, uint64_t workspace_bytes, uint32_t m, uint64_t n_total, uint32_t k, DecodeScratch* out) {
+  if (!workspace || reinterpret_cast<uintptr_t>(workspace) % 256 != 0 || workspace_bytes < decode_scratch_bytes(m, n_total, k))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: workspace must be 256-byte aligned and hold q4k_decode_workspace_bytes");
+  uint32_t const pk = uint32_t((uint64_t(k) + 255) / 256 * 256);
+  uint64_t const G = pk / 32;
+  uint8_t* p = static_cast<uint8_t*>(workspace);
+  out->q8.codes = reinterpret_cast<int8_t*>(p); p += align256(uint64_t(m) * pk);
+  out->q8.scales = reinterpret_cast<float*>(p); p += align256(uint64_t(m) * G * 4);
+  out->q8.sums = reinterpret_cast<int32_t*>(p); p += align256(uint64_t(m) * G * 4);
+  out->q8.codes_len = uint64_t(m) * pk; out->q8.scales_len = out->q8.sums_len = uint64_t(m) * G;
+  out->q8.m = m; out->q8.k = k; out->q8.padded_k = pk;
+  out->rows = reinterpret_cast<float*>(p);
+  out->rows_len = 2 * uint64_t(m) * n_total;
+  return Q4K_OK;
+}
+
+// Geometry and epilogue contract of one descriptor (cuda/decode_mmv.cu:440-505).
+int valid_decode_desc(const q4k_decode_desc* d, bool paired_b, const char* what, uint32_t max_m = 16) {
+  if (!d) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: null %s descriptor", what);
+  if (int st = valid_weight(&d->weight, what)) return st;
+  if (d->activation_policy != Q4K_ACTIVATION_Q8_K32)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: only the Q8-K32 activation policy is built (%s)", what);
+  if (d->m < 1 || d->m > max_m || !d->input || d->input_len != uint64_t(d->m) * d->weight.k)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: %s needs 1..%u bf16 input rows of k columns", what, max_m);
+  uint64_t const cells = uint64_t(d->m) * d->weight.n;
+  switch (d->epilogue) {
+    case Q4K_EPILOGUE_SWIGLU_STORE_BF16:
+      if (!paired_b) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: SwiGLU epilogue requires paired gate/up launch");
+      [[fallthrough]];
+    case Q4K_EPILOGUE_STORE_BF16:
+    case Q4K_EPILOGUE_STORE_FP32:
+      if (d->residual || d->residual_len) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: store epilogue must not supply residual");
+      if (!d->output || d->output_len != cells) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: %s output must hold m*n elements", what);
+      break;
+    case Q4K_EPILOGUE_RESIDUAL_ADD_FP32:
+      if (!d->residual || d->residual_len != cells) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: %s residual must hold m*n floats", what);
+      if (d->output ? d->output_len != cells : d->output_len != 0)
+        return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: %s output must hold m*n floats or be empty (in-place residual update)", what);
+      break;
+    default:
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: unknown epilogue");
+  }
+  return Q4K_OK;
+}
+
+// Projection + epilogue of one descriptor whose input is already quantised.  `rows` is m*n floats of scratch.
+int decode_one(const q4k_decode_desc& d, const q4k_q8_input& q8, float* rows, cudaStream_t stream) {
+  uint64_t const cells = uint64_t(d.m) * d.weight.n;
+  switch (d.epilogue) {
+    case Q4K_EPILOGUE_STORE_FP32:
+      return project_impl(&d.weight, q8, static_cast<float*>(d.output), cells, nullptr, 0, nullptr, stream);
+    case Q4K_EPILOGUE_RESIDUAL_ADD_FP32: {
+      float* const out = d.output ? static_cast<float*>(d.output) : const_cast<float*>(d.residual);
+      return project_impl(&d.weight, q8, out, cells, d.residual, cells, nullptr, stream, true);
+    }
+    case Q4K_EPILOGUE_STORE_BF16: {
+      if (int st = project_impl(&d.weight, q8, rows, cells, nullptr, 0, nullptr, stream)) return st;
+      Q4K_CUDA(q4k::launch_store_bf16(rows, static_cast<uint16_t*>(d.output), cells, stream), "decode_mmv.store_bf16");
+      return Q4K_OK;
+    }
+    default:
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: unknown epilogue");
+  }
+}
+
+int decode_pack(const q4k_decode_desc& d, const DecodeScratch& s, int* failure, cudaStream_t stream) {
+  if (!failure) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: null failure flag");
+  return pack_impl(d.input, false, d.input_len, s.q8, failure, stream);
+}
+}  // namespace
+
+uint64_t q4k_decode_workspace_bytes(uint32_t m, uint64_t n_total, uint32_t k) { return decode_scratch_bytes(m, n_total, k); }
+
+int q4k_decode_mmv(const q4k_decode_desc* desc, void* workspace, uint64_t workspace_bytes, int* failure, void* stream_handle) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (int st = valid_decode_desc(desc, false, "desc")) return st;
+  DecodeScratch s{};
+  if (int st = carve_decode_scratch(workspace, workspace_bytes, desc->m, desc->weight.n, desc->weight.k, &s)) return st;
+  if (int st = decode_pack(*desc, s, failure, stream)) return st;
+  return decode_one(*desc, s.q8, s.rows, stream);
+}
+
+int q4k_decode_mmv_paired(const q4k_decode_desc* a, const q4k_decode_desc* b, void* workspace, uint64_t workspace_bytes,
+                          int* failure, void* stream_handle) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (int st = valid_decode_desc(a, true, "paired A")) return st;
+  if (!b) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv_paired: null B descriptor");
+  bool const swiglu = a->epilogue == Q4K_EPILOGUE_SWIGLU_STORE_BF16;
+  q4k_decode_desc bv = *b;
+  if (swiglu) {  // B declares no output of its own (cuda/decode_mmv.cu:514-521)
+    if (b->output || b->output_len || b->residual || b->residual_len)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv_paired: SwiGLU paired B must not declare a separately materialized output");
+    bv.output = a->output;
+    bv.output_len = a->output_len;
+  }
+  if (int st = valid_decode_desc(&bv, true, "paired B")) return st;
+  if (b->weight.layout != a->weight.layout || b->weight.quantizer != a->weight.quantizer || b->weight.n != a->weight.n ||
+      b->weight.k != a->weight.k || b->epilogue != a->epilogue || b->input != a->input || b->input_len != a->input_len ||
+      b->m != a->m || b->activation_policy != a->activation_policy)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv_paired: paired B must match A shape, layout, input, and epilogue contract");
+  DecodeScratch s{};
+  if (int st = carve_decode_scratch(workspace, workspace_bytes, a->m, a->weight.n, a->weight.k, &s)) return st;
+  if (int st = decode_pack(*a, s, failure, stream)) return st;
+  uint64_t const cells = uint64_t(a->m) * a->weight.n;
+  if (!swiglu) {
+    if (int st = decode_one(*a, s.q8, s.rows, stream)) return st;
+    return decode_one(*b, s.q8, s.rows + cells, stream);
+  }
+  if (int st = project_impl(&a->weight, s.q8, s.rows, cells, nullptr, 0, nullptr, stream)) return st;
+  if (int st = project_impl(&b->weight, s.q8, s.rows + cells, cells, nullptr, 0, nullptr, stream)) return st;
+  Q4K_CUDA(q4k::launch_swiglu_store_bf16(s.rows, s.rows + cells, static_cast<uint16_t*>(a->output), cells, stream),
+           "decode_mmv.swiglu");
+  return Q4K_OK;
+}
+
+// PrefillEngine::project / paired_swiglu (cuda/prefill.hpp:88-96) with the quantise -> MMQ dispatch: the same
+// composition as the decode entries without the 16-row limit.
+int q4k_prefill_project(const q4k_decode_desc* projection, void* workspace, uint64_t workspace_bytes, int* failure,
+                        void* stream_handle) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (int st = valid_decode_desc(projection, false, "projection", Q4K_MAX_TOKENS)) return st;
+  DecodeScratch s{};
+  if (int st = carve_decode_scratch(workspace, workspace_bytes, projection->m, projection->weight.n, projection->weight.k, &s))
+    return st;
+  if (int st = decode_pack(*projection, s, failure, stream)) return st;
+  return decode_one(*projection, s.q8, s.rows, stream);
+}
+
+int q4k_prefill_paired_swiglu(const q4k_weight* gate, const q4k_weight* up, const uint16_t* normalized, uint16_t* swiglu,
+                              uint32_t valid_tokens, void* workspace, uint64_t workspace_bytes, int* failure,
+                              void* stream_handle) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (!gate || !up) return fail(Q4K_ERR_INVALID_ARGUMENT, "paired_swiglu: null weight");
+  q4k_decode_desc a{*gate, normalized, uint64_t(valid_tokens) * gate->k, swiglu, uint64_t(valid_tokens) * gate->n, nullptr, 0,
+                    valid_tokens, Q4K_EPILOGUE_SWIGLU_STORE_BF16, Q4K_ACTIVATION_Q8_K32};
+  q4k_decode_desc b = a;
+  b.weight = *up;
+  if (int st = valid_decode_desc(&a, true, "gate", Q4K_MAX_TOKENS)) return st;
+  if (int st = valid_decode_desc(&b, true, "up", Q4K_MAX_TOKENS)) return st;
+  if (up->n != gate->n || up->k != gate->k || up->layout != gate->layout || up->quantizer != gate->quantizer)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "paired_swiglu: gate and up must have the same shape and layout");
+  DecodeScratch s{};
+  if (int st = carve_decode_scratch(workspace, workspace_bytes, valid_tokens, gate->n, gate->k, &s)) return st;
+  if (int st = decode_pack(a, s, failure, stream)) return st;
+  uint64_t const cells = uint64_t(valid_tokens) * gate->n;
+  if (int st = project_impl(gate, s.q8, s.rows, cells, nullptr, 0, nullptr, stream)) return st;
+  if (int st = project_impl(up, s.q8, s.rows + cells, cells, nullptr, 0, nullptr, stream)) return st;
+  Q4K_CUDA(q4k::launch_swiglu_store_bf16(s.rows, s.rows + cells, swiglu, cells, stream), "paired_swiglu.epilogue");
+  return Q4K_OK;
+}
+
+int q4k_decode_mmv_ranges(const q4k_decode_desc* ranges, uint32_t count, void* workspace, uint64_t workspace_bytes,
+                          int* failure, void* stream_handle) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  if (!ranges || count < 2 || count > 3)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv_ranges: two or three ranges");  // cuda/decode_mmv.cu:790
+  uint64_t n_total = 0;
+  for (uint32_t i = 0; i < count; ++i) {
+    if (int st = valid_decode_desc(&ranges[i], false, "range")) return st;
+    if (ranges[i].input != ranges[0].input || ranges[i].input_len != ranges[0].input_len || ranges[i].m != ranges[0].m ||
+        ranges[i].weight.k != ranges[0].weight.k || ranges[i].weight.layout != ranges[0].weight.layout)
+      return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv_ranges: ranges must share K, input and layout");
+    n_total += ranges[i].weight.n;
+  }
+  DecodeScratch s{};
+  if (int st = carve_decode_scratch(workspace, workspace_bytes, ranges[0].m, n_total, ranges[0].weight.k, &s)) return st;
+  if (int st = decode_pack(ranges[0], s, failure, stream)) return st;
+  uint64_t off = 0;
+  for (uint32_t i = 0; i < count; ++i) {
+    if (int st = decode_one(ranges[i], s.q8, s.rows + off, stream)) return st;
+    off += uint64_t(ranges[i].m) * ranges[i].weight.n;
+  }
+  return Q4K_OK;
+}
 
 int q4k_validate_device_span(const void* pointer, uint64_t bytes, uint32_t alignment, int device) {
   return check_span(Region{pointer, bytes, alignment, "span"}, device);

@@ -102,6 +102,10 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
 cudaError_t launch_peer_wait(uint32_t* const* flags, uint32_t* unsignalled, uint32_t ranks, uint32_t rank,
                              long long limit_cycles, int* status, cudaStream_t stream);
 
+// decode_entry.cu : bf16 store and SwiGLU epilogues over fp32 projection rows.
+cudaError_t launch_store_bf16(const float* in, uint16_t* out, uint64_t count, cudaStream_t stream);
+cudaError_t launch_swiglu_store_bf16(const float* gate, const float* up, uint16_t* out, uint64_t count, cudaStream_t stream);
+
 // abi.cu : process-wide switch set by q4k_set_launch_overlap().  When on, the decode kernels
 // (pack, dp4a, TMA gemv) are launched with programmatic stream serialization: they may start,
 // and the TMA kernel may prefetch weights, while the preceding kernel of the stream drains.

@@ -230,6 +230,66 @@ def peer_wait(flags: Sequence[int], rank: int, limit_cycles: int = 0, stream=Non
     _check(L.load().q4k_peer_wait(C.byref(desc), limit_cycles, _stream(stream)))
 
 
+@dataclass
+class DecodeMmvDesc:
+    """One decode projection (struct DecodeMmvDesc, cuda/decode_mmv.hpp:103-121) under the Q8-K32 activation
+    policy: `input` bf16 [m, k]; `output` bf16 or fp32 [m, n] by epilogue, or None for the in-place residual update."""
+    weight: PrefillWeight
+    input: torch.Tensor
+    output: Optional[torch.Tensor]
+    epilogue: int = L.EPILOGUE_STORE_BF16
+    residual: Optional[torch.Tensor] = None
+    activation_policy: int = L.ACTIVATION_Q8_K32
+
+    def c_struct(self) -> L.DecodeDesc:
+        m = self.input.shape[0] if self.input.dim() == 2 else 1
+        return L.DecodeDesc(self.weight.c_struct(), self.input.data_ptr(), self.input.numel(),
+                            0 if self.output is None else self.output.data_ptr(),
+                            0 if self.output is None else self.output.numel(),
+                            0 if self.residual is None else self.residual.data_ptr(),
+                            0 if self.residual is None else self.residual.numel(), m, self.epilogue, self.activation_policy)
+
+
+def decode_workspace(m: int, n_total: int, k: int, device="cuda") -> torch.Tensor:
+    return torch.empty(L.load().q4k_decode_workspace_bytes(m, n_total, k), dtype=torch.uint8, device=device)
+
+
+def launch_decode_mmv(desc: DecodeMmvDesc, workspace: torch.Tensor, failure: torch.Tensor, stream=None) -> None:
+    """launch_decode_mmv (cuda/decode_mmv.hpp:207-209)."""
+    d = desc.c_struct()
+    _check(L.load().q4k_decode_mmv(C.byref(d), _ptr(workspace), workspace.numel(), _ptr(failure), _stream(stream)))
+
+
+def launch_decode_mmv_paired(a: DecodeMmvDesc, b: DecodeMmvDesc, workspace: torch.Tensor, failure: torch.Tensor,
+                             stream=None) -> None:
+    """launch_decode_mmv_paired (cuda/decode_mmv.hpp:210-211): gate/up sharing one input; SwigluStoreBf16 lives here."""
+    da, db = a.c_struct(), b.c_struct()
+    _check(L.load().q4k_decode_mmv_paired(C.byref(da), C.byref(db), _ptr(workspace), workspace.numel(), _ptr(failure),
+                                          _stream(stream)))
+
+
+def launch_decode_mmv_ranges(ranges: Sequence[DecodeMmvDesc], workspace: torch.Tensor, failure: torch.Tensor,
+                             stream=None) -> None:
+    """launch_decode_mmv_ranges (cuda/decode_mmv.hpp:212-215): two or three output ranges over one input."""
+    arr = (L.DecodeDesc * len(ranges))(*[r.c_struct() for r in ranges])
+    _check(L.load().q4k_decode_mmv_ranges(arr, len(ranges), _ptr(workspace), workspace.numel(), _ptr(failure),
+                                          _stream(stream)))
+
+
+def prefill_project(projection: DecodeMmvDesc, workspace: torch.Tensor, failure: torch.Tensor, stream=None) -> None:
+    """PrefillEngine::project (cuda/prefill.hpp:88-89) for a Q4_K weight: quantise -> MMQ -> PrefillEpilogue."""
+    d = projection.c_struct()
+    _check(L.load().q4k_prefill_project(C.byref(d), _ptr(workspace), workspace.numel(), _ptr(failure), _stream(stream)))
+
+
+def prefill_paired_swiglu(gate: PrefillWeight, up: PrefillWeight, normalized: torch.Tensor, swiglu: torch.Tensor,
+                          workspace: torch.Tensor, failure: torch.Tensor, stream=None) -> None:
+    """PrefillEngine::paired_swiglu (cuda/prefill.hpp:90-93): swiglu = bf16(SiLU(gate x) * (up x))."""
+    g, u = gate.c_struct(), up.c_struct()
+    _check(L.load().q4k_prefill_paired_swiglu(C.byref(g), C.byref(u), _ptr(normalized), _ptr(swiglu), normalized.shape[0],
+                                              _ptr(workspace), workspace.numel(), _ptr(failure), _stream(stream)))
+
+
 def q8_mlp_workspace_bytes(m: int, hidden: int, ffn: int) -> int:
     return L.load().q4k_q8_mlp_workspace_bytes(m, hidden, ffn)
 
