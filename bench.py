@@ -212,30 +212,47 @@ def main():
     x_in = {m: {k: torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16) for k in (5120, 17408)} for m in TOKENS}
     q8 = {m: {k: new_q8_input(m, k, dev) for k in (5120, 17408)} for m in TOKENS}
     failure = torch.zeros(1, dtype=torch.int32, device=dev)
-    outs, gathered = {}, {}
+    # Inputs and outputs are slices of one buffer each, ordered by token count, so that the end-to-end leg
+    # moves a step's activations in one host->device copy and each token count's results in one device->host copy.
+    x_pool = torch.empty(sum(m * (5120 + 17408) for m in TOKENS), dtype=torch.bfloat16, device=dev)
+    off = 0
     for m in TOKENS:
+        for k in (5120, 17408):
+            view = x_pool[off:off + m * k].view(m, k)
+            view.copy_(x_in[m][k])
+            x_in[m][k] = view
+            off += m * k
+    outs, gathered, out_group = {}, {}, {}
+    out_pool = torch.empty(sum(m * shard(n)[1] for m in TOKENS for _, n, _ in SHAPES), dtype=torch.float32, device=dev)
+    off = 0
+    for m in TOKENS:
+        start = off
         for i, (_, n, k) in enumerate(SHAPES):
             _, rows, per = shard(n)
             if rows != per:
                 raise SystemExit(f"{n} rows do not split evenly over {world} ranks in row groups of 8")
-            outs[(m, i)] = torch.empty((m, rows), dtype=torch.float32, device=dev)
+            outs[(m, i)] = out_pool[off:off + m * rows].view(m, rows)
+            off += m * rows
             if world > 1:  # rank g's slice lands in gathered[g]; out[t, g*per + j] = gathered[g, t, j]
                 gathered[(m, i)] = torch.empty((world * m, per), dtype=torch.float32, device=dev)
+        out_group[m] = out_pool[start:off]
 
     # Fused gather: every rank's full [m, n] outputs and one arrival-counter array live in one symmetric
     # allocation, so each projection kernel can store its rows straight into every peer.
     fused = world > 1 and args.gather == "fused"
-    full, full_ptrs, flag_ptrs = {}, {}, []
+    full, full_ptrs, flag_ptrs, full_group = {}, {}, [], {}
     if fused:
         try:
             words = sum(m * n for m in TOKENS for _, n, _ in SHAPES) + 16
             pool, bases, pool_handle = symmetric_pool(words, dev)
             off = 0
             for m in TOKENS:
+                start = off
                 for i, (_, n, _) in enumerate(SHAPES):
                     full[(m, i)] = pool[off:off + m * n].view(m, n)
                     full_ptrs[(m, i)] = [b + 4 * off for b in bases]
                     off += m * n
+                full_group[m] = pool[start:off]
             flag_ptrs = [b + 4 * off for b in bases]
         except Exception as exc:  # symmetric memory can be unavailable; the NCCL path still measures the shards
             fused = False
@@ -266,7 +283,7 @@ def main():
         dp4a for one token otherwise."""
         return "dp4a" if (m == 1 and args.no_overlap) else "tma"
 
-    def one_step(step, count=True, quantise=True, only_kernel=None):
+    def one_step(step, count=True, quantise=True, only_kernel=None, after_group=None):
         for mi, m in enumerate(TOKENS):
             layer = (step * len(TOKENS) + mi) % LAYERS
             if quantise:
@@ -278,19 +295,25 @@ def main():
                 if only_kernel and which_kernel(m, layers[layer][i].n) != only_kernel:
                     continue
                 projection(m, i, layer, count)
+            if after_group is not None and not fused:
+                after_group(m)
         if fused:  # the step's outputs are complete on this rank once every peer has delivered as many projections
             peer_wait(flag_ptrs, rank)
             if count:
                 launches["n"] += 1
+            if after_group is not None:  # gathered rows are complete only after the wait
+                for m in TOKENS:
+                    after_group(m)
 
     stream = torch.cuda.Stream(device=dev)
+    copy_stream = torch.cuda.Stream(device=dev)
 
     def capture(fn, n_steps):
         """Capture n_steps consecutive steps (distinct layer rotation) into one graph."""
         with torch.cuda.stream(stream):
             for s in range(2):
                 fn(s)
-            stream.synchronize()
+            torch.cuda.synchronize(dev)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph, stream=stream):
                 for s in range(n_steps):
@@ -418,23 +441,40 @@ def main():
             per_m[str(m)] = round(b / (mm_ms * 1e-3) / 1e9, 1)
 
     # End to end: host buffers in, host buffers out, copies inside the timed region.
-    result_tensors = full if fused else (gathered if world > 1 else outs)
-    h_in = {m: {k: x_in[m][k].cpu().pin_memory() for k in (5120, 17408)} for m in TOKENS}
-    h_out = {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in result_tensors.items()}
+    # End to end: the step's activations arrive from pinned host memory in one copy; each token count's
+    # results leave in one copy on a second stream as soon as they are complete, overlapping the next
+    # projections; the step ends when the last copy has landed.  (NCCL variant: one copy per gathered tensor.)
+    pooled = fused or world == 1
+    groups = full_group if fused else out_group
+    h_x = x_pool.cpu().pin_memory()
+    h_group = {m: torch.empty(t.shape, dtype=t.dtype).pin_memory() for m, t in groups.items()} if pooled else {}
+    h_out = {} if pooled else {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in gathered.items()}
 
     def e2e_step(s):
-        for m in TOKENS:
-            for k in (5120, 17408):
-                x_in[m][k].copy_(h_in[m][k], non_blocking=True)
-        one_step(s, count=False)
-        for key, t in result_tensors.items():
-            h_out[key].copy_(t, non_blocking=True)
+        x_pool.copy_(h_x, non_blocking=True)
+        main = torch.cuda.current_stream()
+
+        def drain(m):
+            ev = torch.cuda.Event()
+            ev.record(main)
+            copy_stream.wait_event(ev)
+            with torch.cuda.stream(copy_stream):
+                h_group[m].copy_(groups[m], non_blocking=True)
+
+        one_step(s, count=False, after_group=drain if pooled else None)
+        if pooled:
+            done = torch.cuda.Event()
+            done.record(copy_stream)
+            main.wait_event(done)
+        else:
+            for key, t in gathered.items():
+                h_out[key].copy_(t, non_blocking=True)
 
     ge = capture(e2e_step, UNROLL) if use_graph else Eager(e2e_step, UNROLL)
     timed(ge, warm_replays)
     ms_e2e = timed(ge, replays)
     h2d = sum(m * (5120 + 17408) * 2 for m in TOKENS)
-    d2h = sum(t.numel() * 4 for t in h_out.values())
+    d2h = sum(t.numel() * 4 for t in (h_group if pooled else h_out).values())
     e2e_value = total_bytes * steps / (ms_e2e * 1e-3) / 1e9
 
     prefill = None

@@ -100,12 +100,13 @@ uint32_t q4k_abi_version(void);
  * token-major.  Validation follows cuda/decode_mmv.cu:440-540: a store epilogue must not supply a residual;
  * ResidualAddFp32 reads `residual` and writes `output`, or updates `residual` in place when `output` is NULL;
  * SwigluStoreBf16 needs the paired call, whose B side declares no output and shares A's input.
- * The Bf16 policy (bf16-rounded weights x bf16 activations, cuda/decode_mmv.cu:121-250) is not built. */
+ * The reference's own Bf16 policy (weights reconstructed in fp32 and rounded to bf16, fp32 FMA with the bf16
+ * activations, cuda/decode_mmv.cu:121-250) is accepted on the three decode entries as well. */
 #define Q4K_EPILOGUE_STORE_BF16 1
 #define Q4K_EPILOGUE_STORE_FP32 2
 #define Q4K_EPILOGUE_RESIDUAL_ADD_FP32 3
 #define Q4K_EPILOGUE_SWIGLU_STORE_BF16 4 /* paired gate/up only: y = bf16(SiLU(a.x) * b.x) */
-#define Q4K_ACTIVATION_BF16 1            /* reference policy; rejected here */
+#define Q4K_ACTIVATION_BF16 1            /* reference policy: bf16-rounded weights x bf16 activations */
 #define Q4K_ACTIVATION_Q8_K32 2          /* Q8 activations, exact int32 K32 dots */
 
 typedef struct q4k_decode_desc {

@@ -456,8 +456,10 @@ int carve_decode_scratch(void* workspace, uint64_t workspace_bytes, uint32_t m, 
 int valid_decode_desc(const q4k_decode_desc* d, bool paired_b, const char* what, uint32_t max_m = 16) {
   if (!d) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: null %s descriptor", what);
   if (int st = valid_weight(&d->weight, what)) return st;
-  if (d->activation_policy != Q4K_ACTIVATION_Q8_K32)
-    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: only the Q8-K32 activation policy is built (%s)", what);
+  if (d->activation_policy != Q4K_ACTIVATION_Q8_K32 && !(d->activation_policy == Q4K_ACTIVATION_BF16 && max_m <= 16))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: %s activation policy must be Q8-K32 (or Bf16 on the decode entries)", what);
+  if (d->activation_policy == Q4K_ACTIVATION_BF16 && reinterpret_cast<uintptr_t>(d->input) % 2 != 0)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: %s input must be 2-byte aligned", what);
   if (d->m < 1 || d->m > max_m || !d->input || d->input_len != uint64_t(d->m) * d->weight.k)
     return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: %s needs 1..%u bf16 input rows of k columns", what, max_m);
   uint64_t const cells = uint64_t(d->m) * d->weight.n;
@@ -482,17 +484,30 @@ int valid_decode_desc(const q4k_decode_desc* d, bool paired_b, const char* what,
 }
 
 // Projection + epilogue of one descriptor whose input is already quantised.  `rows` is m*n floats of scratch.
+// fp32 rows of one descriptor under its activation policy, residual added last.
+int decode_rows(const q4k_decode_desc& d, const q4k_q8_input& q8, float* out, const float* residual, cudaStream_t stream) {
+  uint64_t const cells = uint64_t(d.m) * d.weight.n;
+  if (d.activation_policy == Q4K_ACTIVATION_Q8_K32)
+    return project_impl(&d.weight, q8, out, cells, residual, residual ? cells : 0, nullptr, stream, true);
+  Region regions[3] = {{d.weight.codes, d.weight.codes_bytes, 4, "weight.codes"},
+                       {d.weight.scales, d.weight.scales_bytes, 2, "weight.scales"},
+                       {out, cells * 4, 4, "output"}};
+  if (int st = check_distinct(regions, 3, false)) return st;
+  Q4K_CUDA(q4k::launch_gemv_bf16w(view(d.weight), d.input, d.m, d.weight.k, d.weight.padded_k, out, residual, stream),
+           "decode_mmv.gemv_bf16w");
+  return Q4K_OK;
+}
+
+// Projection + epilogue of one descriptor whose input is already quantised.  `rows` is m*n floats of scratch.
 int decode_one(const q4k_decode_desc& d, const q4k_q8_input& q8, float* rows, cudaStream_t stream) {
   uint64_t const cells = uint64_t(d.m) * d.weight.n;
   switch (d.epilogue) {
     case Q4K_EPILOGUE_STORE_FP32:
-      return project_impl(&d.weight, q8, static_cast<float*>(d.output), cells, nullptr, 0, nullptr, stream);
-    case Q4K_EPILOGUE_RESIDUAL_ADD_FP32: {
-      float* const out = d.output ? static_cast<float*>(d.output) : const_cast<float*>(d.residual);
-      return project_impl(&d.weight, q8, out, cells, d.residual, cells, nullptr, stream, true);
-    }
+      return decode_rows(d, q8, static_cast<float*>(d.output), nullptr, stream);
+    case Q4K_EPILOGUE_RESIDUAL_ADD_FP32:
+      return decode_rows(d, q8, d.output ? static_cast<float*>(d.output) : const_cast<float*>(d.residual), d.residual, stream);
     case Q4K_EPILOGUE_STORE_BF16: {
-      if (int st = project_impl(&d.weight, q8, rows, cells, nullptr, 0, nullptr, stream)) return st;
+      if (int st = decode_rows(d, q8, rows, nullptr, stream)) return st;
       Q4K_CUDA(q4k::launch_store_bf16(rows, static_cast<uint16_t*>(d.output), cells, stream), "decode_mmv.store_bf16");
       return Q4K_OK;
     }
@@ -502,6 +517,7 @@ int decode_one(const q4k_decode_desc& d, const q4k_q8_input& q8, float* rows, cu
 }
 
 int decode_pack(const q4k_decode_desc& d, const DecodeScratch& s, int* failure, cudaStream_t stream) {
+  if (d.activation_policy == Q4K_ACTIVATION_BF16) return Q4K_OK;  // that policy multiplies the bf16 input as it is
   if (!failure) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: null failure flag");
   return pack_impl(d.input, false, d.input_len, s.q8, failure, stream);
 }
@@ -544,8 +560,8 @@ int q4k_decode_mmv_paired(const q4k_decode_desc* a, const q4k_decode_desc* b, vo
     if (int st = decode_one(*a, s.q8, s.rows, stream)) return st;
     return decode_one(*b, s.q8, s.rows + cells, stream);
   }
-  if (int st = project_impl(&a->weight, s.q8, s.rows, cells, nullptr, 0, nullptr, stream)) return st;
-  if (int st = project_impl(&b->weight, s.q8, s.rows + cells, cells, nullptr, 0, nullptr, stream)) return st;
+  if (int st = decode_rows(*a, s.q8, s.rows, nullptr, stream)) return st;
+  if (int st = decode_rows(bv, s.q8, s.rows + cells, nullptr, stream)) return st;
   Q4K_CUDA(q4k::launch_swiglu_store_bf16(s.rows, s.rows + cells, static_cast<uint16_t*>(a->output), cells, stream),
            "decode_mmv.swiglu");
   return Q4K_OK;
@@ -596,7 +612,8 @@ int q4k_decode_mmv_ranges(const q4k_decode_desc* ranges, uint32_t count, void* w
   for (uint32_t i = 0; i < count; ++i) {
     if (int st = valid_decode_desc(&ranges[i], false, "range")) return st;
     if (ranges[i].input != ranges[0].input || ranges[i].input_len != ranges[0].input_len || ranges[i].m != ranges[0].m ||
-        ranges[i].weight.k != ranges[0].weight.k || ranges[i].weight.layout != ranges[0].weight.layout)
+        ranges[i].weight.k != ranges[0].weight.k || ranges[i].weight.layout != ranges[0].weight.layout ||
+        ranges[i].activation_policy != ranges[0].activation_policy)
       return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv_ranges: ranges must share K, input and layout");
     n_total += ranges[i].weight.n;
   }

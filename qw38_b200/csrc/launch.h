@@ -106,6 +106,10 @@ cudaError_t launch_peer_wait(uint32_t* const* flags, uint32_t* unsignalled, uint
 cudaError_t launch_store_bf16(const float* in, uint16_t* out, uint64_t count, cudaStream_t stream);
 cudaError_t launch_swiglu_store_bf16(const float* gate, const float* up, uint16_t* out, uint64_t count, cudaStream_t stream);
 
+// gemv_bf16w.cu : the reference's Bf16 activation policy (bf16-rounded weights x bf16 activations, fp32 FMA).
+cudaError_t launch_gemv_bf16w(const WeightView& w, const uint16_t* x, uint32_t m, uint32_t k, uint32_t padded_k, float* out,
+                              const float* residual, cudaStream_t stream);
+
 // abi.cu : process-wide switch set by q4k_set_launch_overlap().  When on, the decode kernels
 // (pack, dp4a, TMA gemv) are launched with programmatic stream serialization: they may start,
 // and the TMA kernel may prefetch weights, while the preceding kernel of the stream drains.

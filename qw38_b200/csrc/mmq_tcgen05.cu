@@ -603,7 +603,7 @@ TcPlan plan_tcgen05(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_r
     // prohibitive for a prefill chunk -- the penalty grows with m.
     uint32_t const sms = uint32_t(sm_count());
     uint32_t const max_split = tiles_k / 4 ? (tiles_k / 4 > 16 ? 16 : tiles_k / 4) : 1;
-    double const penalty = 0.01 + 0.2 * (m >= 128 ? 1.0 : double(m) / 128.0);
+    double const penalty = 0.01 + 0.1 * (m >= 128 ? 1.0 : double(m) / 128.0);
     double best = -1.0;
     split = 1;
     for (uint32_t s = 1; s <= max_split; ++s) {

@@ -63,8 +63,8 @@ def test_decode_mmv_epilogues(m):
         launch_decode_mmv(DecodeMmvDesc(w, x, canary, L.EPILOGUE_STORE_FP32, residual=res), ws, f)
     with pytest.raises(Q4KError, match="requires paired"):
         launch_decode_mmv(DecodeMmvDesc(w, x, out16, L.EPILOGUE_SWIGLU_STORE_BF16), ws, f)
-    with pytest.raises(Q4KError, match="Q8-K32"):
-        launch_decode_mmv(DecodeMmvDesc(w, x, canary, L.EPILOGUE_STORE_FP32, activation_policy=L.ACTIVATION_BF16), ws, f)
+    with pytest.raises(Q4KError, match="activation policy"):
+        launch_decode_mmv(DecodeMmvDesc(w, x, canary, L.EPILOGUE_STORE_FP32, activation_policy=7), ws, f)
     with pytest.raises(Q4KError, match="workspace"):
         launch_decode_mmv(DecodeMmvDesc(w, x, canary, L.EPILOGUE_STORE_FP32), ws[:1024], f)
     torch.cuda.synchronize()
@@ -139,4 +139,47 @@ def test_prefill_project_and_paired_swiglu():
     got = bf16_to_f32(bf16_bits(y)).astype(np.float64)
     tol = 2.0 ** -7 * np.abs(want) + 2e-3 * np.sqrt((want ** 2).mean())
     assert (np.abs(got - want) <= tol).all()
+    assert f.item() == 0
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 520, 1280), (3, 137, 259), (1, 1000, 5120)])
+def test_decode_mmv_bf16_policy(m, n, k):
+    """The reference's own activation policy (bf16-rounded weights x bf16 activations): compared with the CPU
+    statement of src/compiler/quantization/reference.cpp at the reference's decode_mmv_tol budget
+    (cuda/decode_mmv.hpp: 1e-3 + 1e-4|ref| for fp32, 8e-3 for the bf16 store), K tail and ragged rows included."""
+    codes, meta = synth.logical_q4k(n, k, seed=31)
+    hc, hs = synth.split_tiles(codes, meta)
+    from qw38_b200.q4k_q8 import PrefillWeight, pad_k
+    w = PrefillWeight.from_host(hc, hs, n, k)
+    xb = synth.f32_to_bf16_bits(synth.activations(m, k, seed=32))
+    x = torch.from_numpy(xb.view(np.int16)).to(DEV).view(torch.bfloat16)
+    ref = np.stack([orc.bf16_gemv(hc, hs, n, k, pad_k(k), xb[t]) for t in range(m)])
+    ws = decode_workspace(m, 2 * n, k)
+    f = torch.zeros(1, dtype=torch.int32, device=DEV)
+    out = torch.empty((m, n), dtype=torch.float32, device=DEV)
+    launch_decode_mmv(DecodeMmvDesc(w, x, out, L.EPILOGUE_STORE_FP32, activation_policy=L.ACTIVATION_BF16), ws, f)
+    got = out.cpu().numpy()
+    scale = np.abs(ref).max()
+    assert (np.abs(got - ref) <= 1e-3 + 1e-4 * np.abs(ref) + 2e-6 * scale * np.sqrt(k)).all()
+    res = torch.from_numpy(synth.activations(m, n, seed=33)).to(DEV)
+    inplace = res.clone()
+    launch_decode_mmv(DecodeMmvDesc(w, x, None, L.EPILOGUE_RESIDUAL_ADD_FP32, residual=inplace, activation_policy=L.ACTIVATION_BF16), ws, f)
+    assert torch.equal(inplace, res + out)
+    y = torch.empty((m, n), dtype=torch.bfloat16, device=DEV)
+    launch_decode_mmv(DecodeMmvDesc(w, x, y, L.EPILOGUE_STORE_BF16, activation_policy=L.ACTIVATION_BF16), ws, f)
+    assert (bf16_bits(y) == synth.f32_to_bf16_bits(got)).all()
+    # paired SwiGLU under the same policy
+    codes2, meta2 = synth.logical_q4k(n, k, seed=34)
+    hc2, hs2 = synth.split_tiles(codes2, meta2)
+    w2 = PrefillWeight.from_host(hc2, hs2, n, k)
+    ref2 = np.stack([orc.bf16_gemv(hc2, hs2, n, k, pad_k(k), xb[t]) for t in range(m)])
+    launch_decode_mmv_paired(DecodeMmvDesc(w, x, y, L.EPILOGUE_SWIGLU_STORE_BF16, activation_policy=L.ACTIVATION_BF16),
+                             DecodeMmvDesc(w2, x, None, L.EPILOGUE_SWIGLU_STORE_BF16, activation_policy=L.ACTIVATION_BF16), ws, f)
+    g, u = ref.astype(np.float64), ref2.astype(np.float64)
+    want = g / (1.0 + np.exp(-g)) * u
+    got_y = bf16_to_f32(bf16_bits(y)).astype(np.float64)
+    assert (np.abs(got_y - want) <= 2.0 ** -7 * np.abs(want) + 8e-3 + 1e-3 * np.abs(u)).all()
+    with pytest.raises(Q4KError, match="must match"):       # policies of a pair must agree
+        launch_decode_mmv_paired(DecodeMmvDesc(w, x, out, L.EPILOGUE_STORE_FP32, activation_policy=L.ACTIVATION_BF16),
+                                 DecodeMmvDesc(w2, x, torch.empty_like(out), L.EPILOGUE_STORE_FP32), ws, f)
     assert f.item() == 0
