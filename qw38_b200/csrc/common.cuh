@@ -77,7 +77,9 @@ __device__ __forceinline__ void announce_deliveries(uint32_t* unsignalled, uint3
   uint32_t const u = *reinterpret_cast<volatile uint32_t*>(unsignalled);
   if (u == 0) return;
   *reinterpret_cast<volatile uint32_t*>(unsignalled) = 0;
-  for (uint32_t g = 0; g < ranks; ++g) atomicAdd_system(peer_flag[g] + rank, u);
+#pragma unroll
+  for (int g = 0; g < 8; ++g)
+    if (g < int(ranks)) atomicAdd_system(peer_flag[g] + rank, u);
 }
 
 }  // namespace q4k

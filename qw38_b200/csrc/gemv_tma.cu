@@ -192,7 +192,11 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       if (!live || row >= p.n) return;
       if (to_slices) { slice_dst[so + row] = v; return; }
       if (p.residual) v += p.residual[oo + row];
-      for (uint32_t g = 0; g < p.ndst; ++g) p.out[g][oo + row] = v;
+      // static indices: a run-time index into the kernel parameters measured 6 us slower per launch
+      p.out[0][oo + row] = v;
+#pragma unroll
+      for (int g = 1; g < 8; ++g)
+        if (g < int(p.ndst)) p.out[g][oo + row] = v;
     };
     for (uint32_t it = 0; it < ntiles; ++it) {
       uint32_t const s = it & slot_mask, use = it >> slot_shift;
@@ -397,7 +401,10 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         for (uint32_t sl = 1; sl < p.split_k; ++sl) v += __ldcg(p.slices + size_t(sl) * p.m * p.n + o);
         size_t const oo = size_t(tok) * p.out_stride + p.out_row0 + row;
         if (p.residual) v += p.residual[oo];
-        for (uint32_t g = 0; g < p.ndst; ++g) p.out[g][oo] = v;
+        p.out[0][oo] = v;
+#pragma unroll
+        for (int g = 1; g < 8; ++g)
+          if (g < int(p.ndst)) p.out[g][oo] = v;
       }
     }
   }
