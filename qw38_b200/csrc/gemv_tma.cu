@@ -181,23 +181,16 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     uint32_t const r = lane >> 2, q = lane & 3;
     pdl_wait();
     if (p.done != nullptr && blockIdx.x == 0 && warp == kFirstReducer && lane == 0) announce_deliveries(p.unsignalled, p.peer_flag, p.ndst, p.rank);
+    // Destination of this warp's values: the K slice's scratch tile, or the output (one buffer, or every
+    // rank's copy of the gathered output).  Offsets are those of (tok0, row 0).
     bool const to_slices = p.split_k > 1;
-    float* const slice_dst = p.slices + size_t(slice) * p.m * p.n;
+    float* const dst = to_slices ? p.slices + size_t(slice) * p.m * p.n : p.out[0];
+    const float* const res = to_slices ? nullptr : p.residual;
+    uint32_t const extra = to_slices ? 0u : p.ndst - 1;   // further destinations (row-sharded gather)
     uint32_t const tok0 = nt * 8 + q * 2;
     bool const live0 = tok0 < p.m, live1 = tok0 + 1 < p.m;
-    // element offsets of (tok0, row 0) in the K slice's scratch tile and in the destinations
-    size_t const s0 = size_t(tok0) * p.n, s1 = s0 + p.n;
-    size_t const o0 = size_t(tok0) * p.out_stride + p.out_row0, o1 = o0 + p.out_stride;
-    auto put = [&](bool live, size_t so, size_t oo, uint32_t row, float v) {
-      if (!live || row >= p.n) return;
-      if (to_slices) { slice_dst[so + row] = v; return; }
-      if (p.residual) v += p.residual[oo + row];
-      // static indices: a run-time index into the kernel parameters measured 6 us slower per launch
-      p.out[0][oo + row] = v;
-#pragma unroll
-      for (int g = 1; g < 8; ++g)
-        if (g < int(p.ndst)) p.out[g][oo + row] = v;
-    };
+    size_t const o0 = to_slices ? size_t(tok0) * p.n : size_t(tok0) * p.out_stride + p.out_row0;
+    size_t const o1 = o0 + (to_slices ? p.n : p.out_stride);
     for (uint32_t it = 0; it < ntiles; ++it) {
       uint32_t const s = it & slot_mask, use = it >> slot_shift;
       if (!mbar_wait(b_rfull + 8 * s, use & 1, abort_flag, p.status, 0x520)) break;
@@ -212,10 +205,35 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       }
       mbar_arrive(b_rempty + 8 * s);
       uint32_t const row = (t0 + it) * 16 + r;
-      put(live0, s0, o0, row, lo.x);
-      put(live1, s1, o1, row, lo.y);
-      put(live0, s0, o0, row + 8, hi.x);
-      put(live1, s1, o1, row + 8, hi.y);
+      bool const in0 = row < p.n, in1 = row + 8 < p.n;
+      size_t const a0 = o0 + row, a1 = o1 + row;
+      float v00 = lo.x, v01 = lo.y, v10 = hi.x, v11 = hi.y;
+      if (res) {
+        if (in0 && live0) v00 += res[a0];
+        if (in0 && live1) v01 += res[a1];
+        if (in1 && live0) v10 += res[a0 + 8];
+        if (in1 && live1) v11 += res[a1 + 8];
+      }
+      if (in0) {
+        if (live0) dst[a0] = v00;
+        if (live1) dst[a1] = v01;
+      }
+      if (in1) {
+        if (live0) dst[a0 + 8] = v10;
+        if (live1) dst[a1 + 8] = v11;
+      }
+      if (extra) {  // row-sharded gather: the same values into the other ranks' buffers
+#pragma unroll
+        for (int g = 1; g < 8; ++g) {
+          if (g <= int(extra)) {
+            float* const peer = p.out[g];
+            if (in0 && live0) peer[a0] = v00;
+            if (in0 && live1) peer[a1] = v01;
+            if (in1 && live0) peer[a0 + 8] = v10;
+            if (in1 && live1) peer[a1 + 8] = v11;
+          }
+        }
+      }
     }
     __threadfence();
   } else if (warp - kFirstConsumer < nact) {
