@@ -283,8 +283,11 @@ def main():
         dp4a for one token otherwise."""
         return "dp4a" if (m == 1 and args.no_overlap) else "tma"
 
-    def one_step(step, count=True, quantise=True, only_kernel=None, after_group=None):
-        for mi, m in enumerate(TOKENS):
+    def one_step(step, count=True, quantise=True, only_kernel=None, after_group=None, largest_first=False):
+        # largest_first: the end-to-end leg runs the big token counts first, so that their device->host
+        # copies overlap the remaining projections and only the smallest copy is left exposed at the end
+        order = list(enumerate(TOKENS))
+        for mi, m in (reversed(order) if largest_first else order):
             layer = (step * len(TOKENS) + mi) % LAYERS
             if quantise:
                 for k in (5120, 17408):
@@ -461,7 +464,7 @@ def main():
             with torch.cuda.stream(copy_stream):
                 h_group[m].copy_(groups[m], non_blocking=True)
 
-        one_step(s, count=False, after_group=drain if pooled else None)
+        one_step(s, count=False, after_group=drain if pooled else None, largest_first=True)
         if pooled:
             done = torch.cuda.Event()
             done.record(copy_stream)

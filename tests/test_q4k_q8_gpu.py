@@ -309,7 +309,7 @@ def test_cluster_split_k_is_deterministic_and_exact(m, split_k, row_groups):
 
 
 @pytest.mark.parametrize("m,split_k,warps", [(1, 0, 0), (3, 1, 20), (7, 2, 0), (8, 3, 7), (8, 0, 5), (9, 0, 0), (13, 2, 12),
-                                             (16, 4, 0), (16, 20, 0)])
+                                             (16, 4, 0), (16, 20, 0), (12, 1, 20), (16, 2, 0)])
 def test_gemv_tma_plans(m, split_k, warps):
     """Weights streamed by TMA, activations in registers: K slices of any width, ragged last slice,
     odd number of row groups, partial dots bit-exact, two runs bitwise equal, status word clean."""
