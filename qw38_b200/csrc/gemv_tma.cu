@@ -6,9 +6,10 @@
 // producer lane issues two bulk tensor copies per stage (code tiles with the 128-byte swizzle,
 // metadata tiles) into a ring that holds most of shared memory.  The work is laid out
 // "K-stationary": consumer warp w owns super-block column sb0 + w of the block's K slice for
-// the whole kernel and keeps everything that depends on (token, K) in registers -- the int8
-// activation fragments of its eight K32 groups, the activation scales, and a * sum split into
-// three tf32 terms -- while the block walks down its range of 16-row tiles.  Per tile a consumer
+// the whole kernel and keeps what depends on (token, K) with it -- the int8 activation fragments
+// of its eight K32 groups and a * sum split into three tf32 terms in registers, the activation
+// scale pairs in a table of its own in shared memory -- while the block walks down its range of
+// 16-row tiles.  Per tile a consumer
 //   * decodes the 16 rows' six-bit scales/mins of its super-block into a small float table,
 //   * ldmatrix's the swizzled code tile into mma A fragments (nibbles -> u8 by mask/shift),
 //   * issues one m16n8k32 u8*s8 MMA per K32 group and token octet whose accumulator input is the
@@ -17,10 +18,16 @@
 //   * folds  a * (sc * dot)  with two packed fp32 FMAs per pair of partials, and the min term
 //     sum_g mn[row,g] * (a*sum)[tok,g] with three m16n8k8 tf32 MMAs (mn is a 6-bit integer and the
 //     three tf32 terms add up to the fp32 value exactly, so the products are exact),
-//   * scales by d / dmin and hands its 16 x m partial tile to the reducer warp, which adds the
-//     consumers' tiles in warp order and writes the rows (or the K slice's scratch tile).
+//   * scales by d / dmin and hands its 16 x 8 partial tile per token octet to that octet's reducer warp,
+//     which adds the consumers' tiles in warp order and writes the rows (or the K slice's scratch tile).
 // K slices of different blocks are added in slice order by the last block to finish a row range
 // (arrival ticket), as in the other split-K kernels of this library.
+//
+// Launched with programmatic stream serialization (launch.h), the producer streams weights while
+// the previous kernel of the stream is still draining; every other role waits for that kernel
+// first.  Row-sharded use (GemvTmaGather): the reducers store each value into every rank's copy
+// of the gathered output with plain peer stores, and the last block counts the projection as
+// finished; the count is announced to the peers by the next kernel of the stream.
 //
 // Contract notes (reference: cuda/q4k_q8.cu:63-112, mmvq): the int32 dot of a K32 group is exact
 // and never carried into the next group; scales stay fp32.  Every mbarrier wait is bounded.

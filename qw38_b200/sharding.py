@@ -2,7 +2,9 @@
 
 Rows are independent (out[row] depends on W[row, :] and x only), so each rank keeps a contiguous
 run of row groups (8 rows, the unit of the split-tile layout), quantises the replicated
-activations itself, and the [m, rows] output slices are all-gathered.  No other exchange."""
+activations itself, and the [m, rows] output slices are gathered: by the projection kernel itself,
+which stores into every rank's buffer (q4k_q8_project_gather over a symmetric_pool allocation), or by
+an NCCL all-gather of the slices.  No other exchange."""
 from __future__ import annotations
 
 from typing import List, Tuple
