@@ -283,7 +283,7 @@ def main():
         dp4a for one token otherwise."""
         return "dp4a" if (m == 1 and args.no_overlap) else "tma"
 
-    def one_step(step, count=True, quantise=True, only_kernel=None, after_group=None, largest_first=False):
+    def one_step(step, count=True, quantise=True, only_kernel=None, after_group=None, largest_first=False, xin=None):
         # largest_first: the end-to-end leg runs the big token counts first, so that their device->host
         # copies overlap the remaining projections and only the smallest copy is left exposed at the end
         order = list(enumerate(TOKENS))
@@ -291,7 +291,7 @@ def main():
             layer = (step * len(TOKENS) + mi) % LAYERS
             if quantise:
                 for k in (5120, 17408):
-                    pack_q8(x_in[m][k], failure, out=q8[m][k])
+                    pack_q8((xin or x_in)[m][k], failure, out=q8[m][k])
                     if count:
                         launches["n"] += 1
             for i in range(len(SHAPES)):
@@ -443,19 +443,38 @@ def main():
             b = sum(algorithmic_bytes(m, n, k, with_quantise=False) for _, n, k in SHAPES) * UNROLL * max(2, replays // 2)
             per_m[str(m)] = round(b / (mm_ms * 1e-3) / 1e9, 1)
 
-    # End to end: host buffers in, host buffers out, copies inside the timed region.
-    # End to end: the step's activations arrive from pinned host memory in one copy; each token count's
-    # results leave in one copy on a second stream as soon as they are complete, overlapping the next
-    # projections; the step ends when the last copy has landed.  (NCCL variant: one copy per gathered tensor.)
+    # End to end: every step's activations arrive from pinned host memory in one copy, issued on a second
+    # stream while the step before it computes (two device buffers alternate); each token count's results
+    # leave in one copy on that stream as soon as they are complete, overlapping the next projections; a step
+    # ends when its last result copy has landed.  (NCCL variant: one copy per gathered tensor, one stream.)
     pooled = fused or world == 1
     groups = full_group if fused else out_group
     h_x = x_pool.cpu().pin_memory()
     h_group = {m: torch.empty(t.shape, dtype=t.dtype).pin_memory() for m, t in groups.items()} if pooled else {}
     h_out = {} if pooled else {key: torch.empty(t.shape, dtype=t.dtype).pin_memory() for key, t in gathered.items()}
+    x_pool_b = x_pool.clone()
+    x_in_b, off = {}, 0
+    for m in TOKENS:
+        x_in_b[m] = {}
+        for k in (5120, 17408):
+            x_in_b[m][k] = x_pool_b[off:off + m * k].view(m, k)
+            off += m * k
+    x_sets = [(x_pool, x_in), (x_pool_b, x_in_b)]
 
     def e2e_step(s):
-        x_pool.copy_(h_x, non_blocking=True)
         main = torch.cuda.current_stream()
+        if not pooled:
+            x_pool.copy_(h_x, non_blocking=True)
+            one_step(s, count=False)
+            for key, t in gathered.items():
+                h_out[key].copy_(t, non_blocking=True)
+            return
+        # the next step's inputs: into the buffer whose last readers (the step before this one) are done
+        start = torch.cuda.Event()
+        start.record(main)
+        copy_stream.wait_event(start)
+        with torch.cuda.stream(copy_stream):
+            x_sets[(s + 1) % 2][0].copy_(h_x, non_blocking=True)
 
         def drain(m):
             ev = torch.cuda.Event()
@@ -464,14 +483,10 @@ def main():
             with torch.cuda.stream(copy_stream):
                 h_group[m].copy_(groups[m], non_blocking=True)
 
-        one_step(s, count=False, after_group=drain if pooled else None, largest_first=True)
-        if pooled:
-            done = torch.cuda.Event()
-            done.record(copy_stream)
-            main.wait_event(done)
-        else:
-            for key, t in gathered.items():
-                h_out[key].copy_(t, non_blocking=True)
+        one_step(s, count=False, after_group=drain, largest_first=True, xin=x_sets[s % 2][1])
+        done = torch.cuda.Event()
+        done.record(copy_stream)
+        main.wait_event(done)
 
     ge = capture(e2e_step, UNROLL) if use_graph else Eager(e2e_step, UNROLL)
     timed(ge, warm_replays)

@@ -144,7 +144,7 @@ int q4k_prefill_paired_swiglu(const q4k_weight* gate, const q4k_weight* up, cons
                               uint32_t valid_tokens, void* workspace, uint64_t workspace_bytes, int* failure, void* stream);
 
 /* Row-sharded decode with the gather fused into the projection (no counterpart in the reference, which is
- * single-GPU; BASELINE north_star: "N is split across 1/2/4/8 GPUs ... all-gather of the output slices").
+ * single-GPU: output rows split over the GPUs of one node, output slices gathered on every GPU).
  * Every rank holds a full [m][total_rows] fp32 output buffer and a zeroed uint32[16] flag array (words 0-7:
  * deliveries per rank; 8-9: this rank's own bookkeeping), both mapped into
  * every other rank's address space (CUDA IPC, VMM or torch symmetric memory; plain peer stores, no

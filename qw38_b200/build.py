@@ -33,10 +33,24 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile every kernel file to objects in parallel and link the shared library."""
-    if not force and not needs_build():
-        return LIB
+    """Compile every kernel file to objects in parallel and link the shared library.
+
+    Several processes may import the package at once (one rank per GPU): the check and the build run under
+    an exclusive file lock, and the library is linked under a temporary name and renamed into place, so a
+    rank either waits for the one that builds or finds a complete library."""
+    import fcntl
     LIB.parent.mkdir(parents=True, exist_ok=True)
+    with open(LIB.parent / ".build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():
+                return LIB
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
     objdir = PKG / "lib" / "obj"
     objdir.mkdir(parents=True, exist_ok=True)
     procs = []
@@ -52,10 +66,12 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if verbose:
             print(out)
         objs.append(str(obj))
-    cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(LIB), *objs]
+    tmp = LIB.with_suffix(f".so.tmp{os.getpid()}")
+    cmd = [nvcc(), "-shared", "-gencode", "arch=compute_100a,code=sm_100a", "-o", str(tmp), *objs]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}{r.stderr}")
+    os.replace(tmp, LIB)
     return LIB
 
 
