@@ -101,6 +101,10 @@ class ClockSampler:
 # ----------------------------------------------------------------------------------------------
 # CPU arm: the oracle port of the reference equation on the host cores
 # ----------------------------------------------------------------------------------------------
+WORKLOAD = ("config[1]: decode projection set QKV 7168x5120, O 5120x5120, gate+up 34816x5120, down 5120x17408, "
+            "Q4_K weights, M in {1,2,4,8,16}, bf16 activations quantised on device")
+
+
 def cpu_sample(repeats: int, rows_per_matrix: int = 256):
     """Times the CPU restatement on a bounded sample: `rows_per_matrix` output rows of every
     matrix of the set, all five token counts, all host cores.  Returns (GB/s, cores, text)."""
@@ -145,7 +149,7 @@ def run_reference_arm(args):
     line = {"impl": "reference", "metric": METRIC, "value": gbps, "unit": "GB/s", "n_gpus": args.gpus,
             "steps": steps, "warmup": warm, "ms_per_step": elapsed / steps * 1e3, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "int8 dot / fp32 affine", "data": "synthetic",
-            "config": {"workload": "config[1] decode projection set, M in {1,2,4,8,16}", "sample": sample},
+            "config": {"workload": WORKLOAD, "sample": sample},
             "cpu_baseline": {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample},
             "e2e": {"value": gbps, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line))
@@ -529,8 +533,7 @@ def main():
         line = {"metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": world, "steps": steps, "warmup": warm_replays * UNROLL,
                 "ms_per_step": ms / steps, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
                 "dtype": "int8 dot / fp32 affine", "data": "synthetic",
-                "config": {"workload": "config[1]: decode projection set QKV 7168x5120, O 5120x5120, gate+up 34816x5120, "
-                                       "down 5120x17408, Q4_K weights, M in {1,2,4,8,16}, bf16 activations quantised on device",
+                "config": {"workload": WORKLOAD,
                            "layers_rotated": LAYERS, "l2": f"weights rotate over {LAYERS} layer copies (1.49 GB) > 126 MB L2",
                            "parallelism": f"rows/{world}" + ((" + peer stores fused into the projection kernel, one bounded "
                                                                      "cross-GPU wait per step") if fused else
