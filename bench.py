@@ -302,15 +302,15 @@ def main():
                 if only_kernel and which_kernel(m, layers[layer][i].n) != only_kernel:
                     continue
                 projection(m, i, layer, count)
-            if after_group is not None and not fused:
+            if after_group is not None:
+                if fused:  # this token count's gathered rows are complete once every peer has delivered them
+                    peer_wait(flag_ptrs, rank)
                 after_group(m)
-        if fused:  # the step's outputs are complete on this rank once every peer has delivered as many projections
+        if fused and after_group is None:
+            # the step's outputs are complete on this rank once every peer has delivered as many projections
             peer_wait(flag_ptrs, rank)
             if count:
                 launches["n"] += 1
-            if after_group is not None:  # gathered rows are complete only after the wait
-                for m in TOKENS:
-                    after_group(m)
 
     stream = torch.cuda.Stream(device=dev)
     copy_stream = torch.cuda.Stream(device=dev)
@@ -450,7 +450,9 @@ def main():
     # End to end: every step's activations arrive from pinned host memory in one copy, issued on a second
     # stream while the step before it computes (two device buffers alternate); each token count's results
     # leave in one copy on that stream as soon as they are complete, overlapping the next projections; a step
-    # ends when its last result copy has landed.  (NCCL variant: one copy per gathered tensor, one stream.)
+    # ends when its last result copy has landed.  With several GPUs every rank receives its inputs, each token
+    # count gets its own cross-GPU wait so that its gathered rows can leave at once, and rank 0 alone reads
+    # the (identical) result back.  (NCCL variant: one copy per gathered tensor, one stream.)
     pooled = fused or world == 1
     groups = full_group if fused else out_group
     h_x = x_pool.cpu().pin_memory()
@@ -480,7 +482,9 @@ def main():
         with torch.cuda.stream(copy_stream):
             x_sets[(s + 1) % 2][0].copy_(h_x, non_blocking=True)
 
-        def drain(m):
+        def drain(m):  # the gathered result is read back once, by rank 0
+            if rank != 0:
+                return
             ev = torch.cuda.Event()
             ev.record(main)
             copy_stream.wait_event(ev)
