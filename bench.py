@@ -551,8 +551,8 @@ def main():
                 "roofline": {"bound": "hbm", "kernel": kernel_name, "achieved": achieved, "peak": hbm_peak, "unit": "GB/s",
                              "frac": achieved / hbm_peak, "peak_source": peak_src,
                              # DRAM read+write of one launch = algorithmic bytes x the ratio measured by ncu on the
-                             # 34816x5120 captures under profiles/ (1.05 TMA kernel at M=8, 1.03 dp4a at M=1)
-                             "traffic": pkk["bytes_per_launch"] * (1.05 if dom == "tma" else 1.03),
+                             # 34816x5120 captures under profiles/ (1.06 TMA kernel at M=8, 1.03 dp4a at M=1)
+                             "traffic": pkk["bytes_per_launch"] * (1.06 if dom == "tma" else 1.03),
                              "avg_launch_us": pkk["avg_us"], "bytes_per_launch": pkk["bytes_per_launch"],
                              "by_kernel": {kk: {"GBps": round(v["GBps"], 1), "frac": round(v["GBps"] / hbm_peak, 4),
                                                 "avg_us": round(v["avg_us"], 3), "launches": v["launches"]}
