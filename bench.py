@@ -528,6 +528,26 @@ def main():
                                           "frac_of_2x_measured_bf16": round(tops / int8_peak, 4),
                                           "frac_of_nominal_4500": round(tops / 4500.0, 4)}
             del w, out, xq
+        # config[3]: packed ragged batch, 48 single-row requests + 512 + 237 + 1024 rows = 1821 rows
+        from qw38_b200.q4k_q8 import q4k_q8_project_ragged
+        offs = list(range(49)) + [560, 797, 1821]
+        m, n, k = 1821, 34816, 5120
+        w = synth.device_weight(n, k, seed=98, device=dev)
+        xq = pack_q8(torch.randn((m, k), device=dev, generator=g).to(torch.bfloat16) * 0.5, failure)
+        out = torch.empty((m, n), dtype=torch.float32, device=dev)
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                q4k_q8_project_ragged(w, xq, offs, out=out)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(10):
+                q4k_q8_project_ragged(w, xq, offs, out=out)
+            e1.record(stream)
+        stream.synchronize()
+        t = e0.elapsed_time(e1) / 10
+        prefill["ragged_M1821_N34816_K5120"] = {"ms": round(t, 4), "int8_TOPS": round(2.0 * m * n * k / (t * 1e-3) / 1e12, 1),
+                                                "kernel": "mmq_tcgen05_kernel", "requests": len(offs) - 1}
+        del w, out, xq
 
     if rank == 0:
         dom = max(per_kernel, key=lambda kk: per_kernel[kk]["ms"])
