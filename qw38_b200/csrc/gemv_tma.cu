@@ -43,9 +43,10 @@ namespace {
 constexpr uint32_t kMagicI = 0x4B400000u;  // bit pattern of 1.5 * 2^23
 constexpr float kMagicF = 12582912.0f;
 constexpr int kProducer = 0, kFirstReducer = 1;  // then NT reducer warps, then the consumers
-// per consumer warp: 1280 scale pairs (16 rows, stride 80 bytes so that the eight rows a load touches fall in
-// different banks), 768 mins (row stride 12 floats), 256 d/dmin, then NT * 256 activation scale pairs
-constexpr int kTabBytes = 2304, kTabMn = 1280, kTabDd = 2048;
+// Per consumer warp: 16 rows of 112 bytes -- 64 of scale pairs, 32 of mins, 16 of {d, d, -dmin, -dmin}; the
+// stride of 28 words puts the eight rows a load touches in different banks -- then NT * 256 bytes of
+// activation scale pairs.
+constexpr int kTabRow = 112, kTabMn = 64, kTabDd = 96, kTabBytes = 16 * kTabRow;
 constexpr int kMaxStages = 8;
 
 struct GtParams {
@@ -294,8 +295,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     // groups 0..3: byte & 0x3f; groups 4..7: (byte of word 3 & 0x0f) | ((byte >> 2) & 0x30)  (mins: high nibble of word 3)
     uint32_t const dsh = dh ? 2u : 0u, dmask_a = dh ? 0x30303030u : 0x3f3f3f3fu, dmask_b = dh ? 0x0f0f0f0fu : 0u;
     uint32_t const dec_meta = s_meta + (drow >> 3) * cw * 128 + w * 128 + (drow & 7) * 16;
-    uint32_t const dec_sc = tab + drow * 80 + dh * 32, dec_mn = tab + kTabMn + drow * 48 + dh * 16, dec_dd = tab + kTabDd + drow * 16;
-    uint32_t const rd_sc = tab + r * 80, rd_mn = tab + kTabMn + r * 48 + q * 4, rd_dd = tab + kTabDd + r * 16;
+    uint32_t const dec_sc = tab + drow * kTabRow + dh * 32, dec_mn = dec_sc - dh * 16 + kTabMn, dec_dd = tab + drow * kTabRow + kTabDd;
+    uint32_t const rd_sc = tab + r * kTabRow, rd_mn = rd_sc + kTabMn + q * 4, rd_dd = rd_sc + kTabDd;
     // ldmatrix lane address: matrix j = lane >> 3 (bit 0: row group, bit 1: second K32 group), row i = lane & 7
     uint32_t const lj = lane >> 3, li = lane & 7;
     uint32_t const ld_base = s_codes + (lj & 1) * cw * 1024 + w * 1024 + li * 128;
@@ -343,7 +344,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         // release semantics, so the loads above are performed before it).
         if (gp == 3) mbar_arrive(b_empty + 8 * s);
         float4 const sc_lo = lds128f(rd_sc + gp * 16);         // row r:   {s_g, s_g, s_g+1, s_g+1}
-        float4 const sc_hi = lds128f(rd_sc + 640 + gp * 16);   // row r+8
+        float4 const sc_hi = lds128f(rd_sc + 8 * kTabRow + gp * 16);   // row r+8
         float4 ap4[NT];
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) ap4[nt] = lds128f(rd_ap + (nt * 4 + gp) * 64);
@@ -377,7 +378,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       }
       // ---- min term: rows x groups (6-bit integers) times groups x tokens (three tf32 terms of a*sum) ----
       {
-        uint32_t const m0 = lds32(rd_mn), m1 = lds32(rd_mn + 384), m2 = lds32(rd_mn + 16), m3 = lds32(rd_mn + 400);
+        uint32_t const m0 = lds32(rd_mn), m1 = lds32(rd_mn + 8 * kTabRow), m2 = lds32(rd_mn + 16), m3 = lds32(rd_mn + 8 * kTabRow + 16);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
 #pragma unroll
@@ -385,7 +386,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         }
       }
       float4 const dd_lo = lds128f(rd_dd);        // {d, d, -dmin, -dmin} of row r
-      float4 const dd_hi = lds128f(rd_dd + 128);  // row r+8
+      float4 const dd_hi = lds128f(rd_dd + 8 * kTabRow);  // row r+8
       // ---- hand the tile to the reducer ----
       uint32_t const rs = it & slot_mask, ruse = it >> slot_shift;
       if (ruse > 0 && !mbar_wait(b_rempty + 8 * rs, (ruse - 1) & 1, abort_flag, p.status, 0x540)) break;
