@@ -166,10 +166,12 @@ def main():
     ap.add_argument("--impl", default="b200")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-prefill", action="store_true", help="skip the prefill extra keys")
-    ap.add_argument("--only", default="", help="debug: run a single part (decode)")
+    ap.add_argument("--only", default="", help="debug / profiling: \"decode\" runs the device-resident timing only "
+                                                "(no per-token-count pass, no end-to-end leg, no prefill extras)")
     ap.add_argument("--gather", default="fused", choices=["fused", "nccl"],
                     help="N > 1: projection kernels store into every rank's output over NVLink (fused), or "
                          "NCCL all-gather after each projection")
+    ap.add_argument("--no-graph", action="store_true", help="debug / profiling: eager launches instead of CUDA graph replay")
     ap.add_argument("--no-overlap", action="store_true",
                     help="launch every kernel fully serialised (no programmatic dependent launch)")
     args = ap.parse_args()
@@ -375,9 +377,9 @@ def main():
 
     # A graph holds UNROLL steps so that the LAYERS weight copies are all visited.
     UNROLL = LAYERS
-    use_graph = True
+    use_graph = not args.no_graph
     try:
-        graph = capture(lambda s: one_step(s, count=False), UNROLL)
+        graph = capture(lambda s: one_step(s, count=False), UNROLL) if use_graph else None
     except Exception as exc:  # NCCL capture can be refused; fall back to eager launches
         if world == 1:
             raise
@@ -496,9 +498,12 @@ def main():
         done.record(copy_stream)
         main.wait_event(done)
 
-    ge = capture(e2e_step, UNROLL) if use_graph else Eager(e2e_step, UNROLL)
-    timed(ge, warm_replays)
-    ms_e2e = timed(ge, replays)
+    if args.only:  # debug / profiler runs of the device-resident part alone: no end-to-end number
+        ms_e2e = float("nan")
+    else:
+        ge = capture(e2e_step, UNROLL) if use_graph else Eager(e2e_step, UNROLL)
+        timed(ge, warm_replays)
+        ms_e2e = timed(ge, replays)
     h2d = sum(m * (5120 + 17408) * 2 for m in TOKENS)
     d2h = sum(t.numel() * 4 for t in (h_group if pooled else h_out).values())
     e2e_value = total_bytes * steps / (ms_e2e * 1e-3) / 1e9
