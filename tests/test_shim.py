@@ -23,3 +23,21 @@ def test_shim_compiles_links_and_rejects(tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and "shim check ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_shim_runs_the_path_on_the_device(tmp_path):
+    """pack_q8 -> q4k_q8_project and launch_decode_mmv through the C++ shim, on weights that are all ones."""
+    gxx = shutil.which("g++")
+    cuda = Path("/usr/local/cuda")
+    if gxx is None or not (cuda / "include" / "cuda_runtime.h").exists():
+        pytest.skip("no g++ or CUDA headers")
+    lib = build.build()
+    exe = tmp_path / "shim_gpu"
+    cmd = [gxx, "-std=c++23", "-Wall", "-Wextra", f"-I{ROOT / 'include'}", f"-I{cuda / 'include'}",
+           str(ROOT / "tests" / "shim" / "shim_gpu.cpp"), "-o", str(exe), f"-L{lib.parent}", "-lq4k_b200",
+           f"-L{cuda / 'lib64'}", "-lcudart", f"-Wl,-rpath,{lib.parent}", f"-Wl,-rpath,{cuda / 'lib64'}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and "shim gpu check ok" in r.stdout, r.stdout + r.stderr
