@@ -271,6 +271,31 @@ int q4k_repack_blocks144(const uint8_t* blocks, uint64_t blocks_bytes, uint32_t 
                          uint8_t* out_codes, uint64_t out_codes_bytes, uint8_t* out_scales,
                          uint64_t out_scales_bytes, void* stream);
 
+/* Q4_K fitter on the device: compiler::quantize_q4k_block (src/compiler/quantization/q4k.cpp:186-278)
+ * over every 256 consecutive weights, bit for bit (codes and the 16 metadata bytes).  The reference
+ * runs it on the host, one block after another (quantize_fp32, src/compiler/quantization/quantizer.cpp:173-182).
+ * weights: device memory, fp32 (Q4K_FIT_FP32) or bf16 bits (Q4K_FIT_BF16; widened exactly, as the
+ * reference's compiler does before fitting).  block_status (optional, device, one byte per block)
+ * receives the reason a block was refused -- the reference's error for the first refused block in
+ * index order is the status of the lowest such index; *failure (device int) is set to 1 if any
+ * block was refused, and a refused block is written as zeros.  Asynchronous on `stream`. */
+#define Q4K_FIT_FP32 0u
+#define Q4K_FIT_BF16 1u
+#define Q4K_FIT_OK 0          /* fitted */
+#define Q4K_FIT_NONFINITE 1   /* "Q4_K input is nonfinite" */
+#define Q4K_FIT_RANGE 2       /* "Q4_K fitting range exceeded" (|w| > 1e10) */
+#define Q4K_FIT_RECIPROCAL 3  /* "Q4_K fitting reciprocal overflow" */
+#define Q4K_FIT_COMPRESS 4    /* "Q4_K compression reciprocal overflow" */
+#define Q4K_FIT_HALF 5        /* "Q4_K FP16 scale overflow" */
+/* Logical form: codes int8 [blocks][256] (levels 0..15), metadata [blocks][16]. */
+int q4k_fit_blocks(const void* weights, uint32_t weights_dtype, uint64_t blocks, int8_t* codes,
+                   uint8_t* metadata, uint8_t* block_status, int* failure, void* stream);
+/* Row-major weights [n][k] (k % 256 == 0) straight to the split-tile layout: the fitter and
+ * format::pack_cuda_v0 (src/format/pack.cpp:175-222) in one pass; block b = row * (k/256) + kb. */
+int q4k_fit_weight(const void* weights, uint32_t weights_dtype, uint32_t n, uint32_t k,
+                   uint8_t* out_codes, uint64_t out_codes_bytes, uint8_t* out_scales,
+                   uint64_t out_scales_bytes, uint8_t* block_status, int* failure, void* stream);
+
 /* q8_mlp_workspace_bytes (cuda/q4k_q8.hpp:28-30), generalised from 17408/5120 to (ffn, hidden). */
 uint64_t q4k_q8_mlp_workspace_bytes(uint32_t m, uint32_t hidden, uint32_t ffn);
 

@@ -118,6 +118,37 @@ int ref_quantize_q4k_block(float const* w256, std::int8_t* codes256, std::uint8_
   return st ? 0 : 1;
 }
 
+// The same over `blocks` consecutive 256-weight blocks, every block attempted.  status[b] = 0 when
+// block b was fitted, else the refusal by its message: 1 nonfinite input, 2 fitting range exceeded,
+// 3 fitting reciprocal overflow, 4 compression reciprocal overflow, 5 FP16 scale overflow (9 = other).
+// Refused blocks are left as zeros.  Returns the number of refused blocks.
+std::uint64_t ref_quantize_q4k_blocks(float const* w, std::uint64_t blocks, std::int8_t* codes,
+                                      std::uint8_t* meta, std::uint8_t* status) {
+  static constexpr char const* kMessages[5] = {
+      "Q4_K input is nonfinite", "Q4_K fitting range exceeded", "Q4_K fitting reciprocal overflow",
+      "Q4_K compression reciprocal overflow", "Q4_K FP16 scale overflow"};
+  std::uint64_t refused = 0;
+  for (std::uint64_t b = 0; b < blocks; ++b) {
+    std::int8_t c[256] = {};
+    std::uint8_t m[16] = {};
+    auto st = compiler::quantize_q4k_block(std::span<float const, 256>(w + b * 256, 256),
+                                           std::span<std::int8_t, 256>(c, 256),
+                                           std::span<std::uint8_t, 16>(m, 16));
+    status[b] = 0;
+    if (!st) {
+      ++refused;
+      status[b] = 9;
+      for (int i = 0; i < 5; ++i)
+        if (st.error().detail == kMessages[i]) status[b] = static_cast<std::uint8_t>(i + 1);
+      std::memset(c, 0, sizeof c);
+      std::memset(m, 0, sizeof m);
+    }
+    std::memcpy(codes + b * 256, c, 256);
+    std::memcpy(meta + b * 16, m, 16);
+  }
+  return refused;
+}
+
 // Pinned upstream bodies (third_party/llama.cpp-q4k/reference.hpp:183-275):
 // 144-byte super-blocks from floats, and floats back.
 void ref_llama_quantize_row_q4k(float const* x, std::uint8_t* blocks144, std::int64_t k) {

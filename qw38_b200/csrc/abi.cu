@@ -696,6 +696,44 @@ int q4k_repack_blocks144(const uint8_t* blocks, uint64_t blocks_bytes, uint32_t 
   return Q4K_OK;
 }
 
+int q4k_fit_blocks(const void* weights, uint32_t weights_dtype, uint64_t blocks, int8_t* codes, uint8_t* metadata,
+                   uint8_t* block_status, int* failure, void* stream) {
+  if (!blocks || blocks > 0xffffffffull || weights_dtype > Q4K_FIT_BF16 || !failure)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q4k.fit: invalid geometry");
+  bool const bf16 = weights_dtype == Q4K_FIT_BF16;
+  Region regions[5] = {{weights, blocks * 256 * (bf16 ? 2 : 4), 16, "weights"},
+                       {codes, blocks * 256, 16, "codes"},
+                       {metadata, blocks * 16, 16, "metadata"},
+                       {failure, sizeof(int), 4, "failure"},
+                       {block_status, blocks, 1, "block_status"}};
+  if (int st = check_distinct(regions, block_status ? 5 : 4, false)) return st;
+  Q4K_CUDA(q4k::launch_fit_q4k(weights, bf16, uint32_t(blocks), 1, false, reinterpret_cast<uint8_t*>(codes), metadata,
+                               block_status, failure, static_cast<cudaStream_t>(stream)),
+           "q4k.fit");
+  return Q4K_OK;
+}
+
+int q4k_fit_weight(const void* weights, uint32_t weights_dtype, uint32_t n, uint32_t k, uint8_t* out_codes,
+                   uint64_t out_codes_bytes, uint8_t* out_scales, uint64_t out_scales_bytes, uint8_t* block_status,
+                   int* failure, void* stream) {
+  if (!n || n > Q4K_MAX_N || !k || k > Q4K_MAX_K || k % 256 != 0 || weights_dtype > Q4K_FIT_BF16 || !failure ||
+      out_codes_bytes != q4k_code_bytes(uint32_t(q4k_pad_n(n)), k) ||
+      out_scales_bytes != q4k_scale_bytes(uint32_t(q4k_pad_n(n)), k))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q4k.fit: invalid geometry");
+  bool const bf16 = weights_dtype == Q4K_FIT_BF16;
+  uint64_t const blocks = uint64_t(n) * (k / 256);
+  Region regions[5] = {{weights, blocks * 256 * (bf16 ? 2 : 4), 16, "weights"},
+                       {out_codes, out_codes_bytes, 16, "codes"},
+                       {out_scales, out_scales_bytes, 16, "scales"},
+                       {failure, sizeof(int), 4, "failure"},
+                       {block_status, blocks, 1, "block_status"}};
+  if (int st = check_distinct(regions, block_status ? 5 : 4, false)) return st;
+  Q4K_CUDA(q4k::launch_fit_q4k(weights, bf16, n, k / 256, true, out_codes, out_scales, block_status, failure,
+                               static_cast<cudaStream_t>(stream)),
+           "q4k.fit");
+  return Q4K_OK;
+}
+
 uint64_t q4k_q8_mlp_workspace_bytes(uint32_t m, uint32_t hidden, uint32_t ffn) {
   (void)hidden;  // the hidden-width pack reuses the front of the ffn-width pack
   return uint64_t(m) * (uint64_t(ffn) + uint64_t(ffn) / 32 * 8 + 2ull * ffn * 4) + 4;

@@ -136,6 +136,11 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 int set_error(int code, const char* fmt, ...);
 int set_error_cuda(cudaError_t status, const char* operation);
 
+// fit_q4k.cu: weights [rows][tiles_k*256] (fp32, or bf16 bits) -> Q4_K.  split = false writes int8 codes
+// [blocks][256] + metadata [blocks][16]; split = true writes the split-tile layout for ceil8(rows) rows.
+cudaError_t launch_fit_q4k(const void* weights, bool bf16, uint32_t rows, uint32_t tiles_k, bool split, uint8_t* codes,
+                           uint8_t* meta, uint8_t* status, int* failure, cudaStream_t stream);
+
 // repack.cu
 cudaError_t launch_repack_blocks144(const uint8_t* blocks, uint32_t n, uint32_t k, uint8_t* codes,
                                     uint8_t* meta, cudaStream_t stream);

@@ -340,6 +340,73 @@ def export_q8_1(x: Q8Input, stream=None) -> torch.Tensor:
     return rec
 
 
+FIT_ERRORS = {
+    1: "Q4_K input is nonfinite",
+    2: "Q4_K fitting range exceeded",
+    3: "Q4_K fitting reciprocal overflow",
+    4: "Q4_K compression reciprocal overflow",
+    5: "Q4_K FP16 scale overflow",
+}
+
+
+def _fit_dtype(weights: torch.Tensor) -> int:
+    if weights.dtype == torch.float32:
+        return 0
+    if weights.dtype == torch.bfloat16:
+        return 1
+    raise Q4KError(2, "q4k.fit: weights must be float32 or bfloat16")
+
+
+def _fit_raise(failure: torch.Tensor, status: torch.Tensor) -> None:
+    """The reference stops at the first refused block in index order and returns its error
+    (src/compiler/quantization/quantizer.cpp:176-181)."""
+    if int(failure.item()):
+        bad = torch.nonzero(status)[0]
+        code = int(status[bad].item())
+        raise Q4KError(2, f"q4k.fit: block {int(bad.item())}: {FIT_ERRORS.get(code, code)}")
+
+
+def quantize_q4k_blocks(weights: torch.Tensor, stream=None, check: bool = True):
+    """compiler::quantize_q4k_block (src/compiler/quantization/q4k.cpp:186-278) over every 256
+    consecutive weights of a contiguous device tensor.  Returns (codes int8 [blocks, 256],
+    metadata uint8 [blocks, 16], status uint8 [blocks]); with check (synchronises) a refused block
+    raises the reference's message."""
+    dtype = _fit_dtype(weights)
+    if weights.numel() == 0 or weights.numel() % 256 or not weights.is_contiguous():
+        raise Q4KError(2, "q4k.fit: weights must be contiguous and a multiple of 256 long")
+    blocks = weights.numel() // 256
+    dev = weights.device
+    codes = torch.empty((blocks, 256), dtype=torch.int8, device=dev)
+    meta = torch.empty((blocks, 16), dtype=torch.uint8, device=dev)
+    status = torch.empty(blocks, dtype=torch.uint8, device=dev)
+    failure = torch.zeros(1, dtype=torch.int32, device=dev)
+    _check(L.load().q4k_fit_blocks(_ptr(weights), dtype, blocks, _ptr(codes), _ptr(meta), _ptr(status), _ptr(failure),
+                                   _stream(stream)))
+    if check:
+        _fit_raise(failure, status)
+    return codes, meta, status
+
+
+def quantize_q4k_weight(weights: torch.Tensor, stream=None, check: bool = True) -> PrefillWeight:
+    """Row-major [n, k] float32/bfloat16 device weights (k % 256 == 0) -> split-tile Q4_K weight:
+    the fitter followed by format::pack_cuda_v0 (src/format/pack.cpp:175-222), in one kernel."""
+    dtype = _fit_dtype(weights)
+    if weights.dim() != 2 or not weights.is_contiguous():
+        raise Q4KError(2, "q4k.fit: weights must be a contiguous [n, k] matrix")
+    n, k = weights.shape
+    pn = pad_n(n)
+    dev = weights.device
+    codes = torch.empty(pn * k // 2, dtype=torch.uint8, device=dev)
+    scales = torch.empty(pn * (k // 256) * 16, dtype=torch.uint8, device=dev)
+    status = torch.empty(max(1, n * (k // 256)), dtype=torch.uint8, device=dev)
+    failure = torch.zeros(1, dtype=torch.int32, device=dev)
+    _check(L.load().q4k_fit_weight(_ptr(weights), dtype, n, k, _ptr(codes), codes.numel(), _ptr(scales), scales.numel(),
+                                   _ptr(status), _ptr(failure), _stream(stream)))
+    if check:
+        _fit_raise(failure, status)
+    return PrefillWeight(codes, scales, n, k)
+
+
 def repack_blocks144(blocks: torch.Tensor, n: int, k: int, stream=None) -> PrefillWeight:
     """144-byte llama.cpp-native super-blocks (device uint8) -> split tiles."""
     pn = pad_n(n)

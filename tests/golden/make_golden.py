@@ -107,6 +107,19 @@ def main() -> None:
             sc[i, j], mn[i, j] = a.value, b.value
     out.update(d_q12=q12, d_sc=sc, d_mn=mn)
 
+    # --- E. Fitter corner cases and refusals (quantize_q4k_block, every block attempted). -------
+    from tests.helpers import fitter_cases
+    cases = np.ascontiguousarray(fitter_cases(20240612, 103))
+    nb = cases.shape[0]
+    e_codes = np.zeros((nb, 256), dtype=np.int8)
+    e_meta = np.zeros((nb, 16), dtype=np.uint8)
+    e_status = np.zeros(nb, dtype=np.uint8)
+    ref.ref_quantize_q4k_blocks.restype = C.c_uint64
+    refused = ref.ref_quantize_q4k_blocks(p(cases), C.c_uint64(nb), p(e_codes), p(e_meta), p(e_status))
+    assert refused == int((e_status != 0).sum()) and 9 not in e_status
+    print("fitter cases:", nb, "refused by kind:", np.bincount(e_status, minlength=6)[1:])
+    out.update(e_weights=cases, e_fit_codes=e_codes, e_fit_meta=e_meta, e_fit_status=e_status)
+
     path = Path(__file__).with_name("q4k_ref_vectors.npz")
     np.savez_compressed(path, **out)
     print("wrote", path, path.stat().st_size, "bytes")
