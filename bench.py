@@ -554,6 +554,26 @@ def main():
                                                 "kernel": "mmq_tcgen05_kernel", "requests": len(offs) - 1}
         del w, out, xq
 
+    fitter = None
+    if world == 1 and not args.no_prefill and not args.only:
+        # Offline step of the same path: bf16 weights -> split-tile Q4_K on the device (the reference fits on the host).
+        from qw38_b200.q4k_q8 import quantize_q4k_weight
+        n, k = 5120, 17408
+        wf = (torch.randn((n, k), device=dev, generator=g) * 0.02).to(torch.bfloat16)
+        with torch.cuda.stream(stream):
+            for _ in range(2):
+                quantize_q4k_weight(wf, check=False)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(5):
+                quantize_q4k_weight(wf, check=False)
+            e1.record(stream)
+        stream.synchronize()
+        t = e0.elapsed_time(e1) / 5
+        fitter = {"workload": f"fit bf16 {n}x{k} -> split-tile Q4_K", "ms": round(t, 3), "kernel": "fit_q4k_kernel",
+                  "Mblocks_per_s": round(n * k / 256 / (t * 1e-3) / 1e6, 1)}
+        del wf
+
     if rank == 0:
         dom = max(per_kernel, key=lambda kk: per_kernel[kk]["ms"])
         pkk = per_kernel[dom]
@@ -582,7 +602,7 @@ def main():
                              "by_kernel": {kk: {"GBps": round(v["GBps"], 1), "frac": round(v["GBps"] / hbm_peak, 4),
                                                 "avg_us": round(v["avg_us"], 3), "launches": v["launches"]}
                                            for kk, v in per_kernel.items()}},
-                "decode_GBps_by_tokens": per_m, "prefill": prefill}
+                "decode_GBps_by_tokens": per_m, "prefill": prefill, "fitter": fitter}
         if not args.no_cpu and world == 1:
             gbps, cores, sample = cpu_sample(3)
             line["cpu_baseline"] = {"value": gbps, "unit": "GB/s", "cores": cores, "kind": "port", "sample": sample}

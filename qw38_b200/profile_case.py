@@ -1,11 +1,19 @@
 """Runs one projection a few times so that a profiler can capture a single kernel:
     python -m qw38_b200.profile_case <n> <k> <m> <kernel id> [split_k] [row_groups]
-Kernel ids are the Q4K_KERNEL_* values of include/q4k_b200.h (1 dp4a, 2 mma, 3 tcgen05, 4 cluster mma)."""
+Kernel ids are the Q4K_KERNEL_* values of include/q4k_b200.h (1 dp4a, 2 mma, 3 tcgen05, 4 cluster mma, 5 TMA gemv).
+    python -m qw38_b200.profile_case fit <n> <k>      runs the Q4_K fitter on fp32 [n, k] weights instead."""
 import sys, os
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import torch
 from qw38_b200 import synth
-from qw38_b200.q4k_q8 import pack_q8, q4k_q8_project
+from qw38_b200.q4k_q8 import pack_q8, q4k_q8_project, quantize_q4k_weight
+if sys.argv[1] == "fit":
+    wf = torch.randn((int(sys.argv[2]), int(sys.argv[3])), device="cuda") * 0.02
+    for _ in range(3):
+        pw = quantize_q4k_weight(wf, check=False)
+    torch.cuda.synchronize()
+    print("ok", int(pw.codes.sum()))
+    sys.exit(0)
 n, k, m, kern = (int(a) for a in sys.argv[1:5])
 sk = int(sys.argv[5]) if len(sys.argv) > 5 else 0
 rg = int(sys.argv[6]) if len(sys.argv) > 6 else 0
