@@ -3,7 +3,8 @@
 // Mirrors the operator interface of the reference engine for this path -- cuda/q4k_q8.hpp:14-49
 // (Q8Input, pack_q8, q4k_q8_project, q4k_q8_mlp, q8_mlp_workspace_bytes), cuda/prefill.hpp:33-44
 // (PrefillWeight) and cuda/decode_mmv.hpp:45-51,103-121,207-215 (DecodeEpilogue, DecodeMmvDesc,
-// launch_decode_mmv / _paired / _ranges) -- with the same names, argument meaning and error
+// launch_decode_mmv / _paired / _ranges) and, for the offline step, compiler::quantize_q4k_block
+// (src/compiler/quantization/q4k.hpp) as a batched device call -- with the same names, argument meaning and error
 // behaviour: every call returns std::expected<void, Error>, Error carries the reference's
 // ErrorCode (cuda/error.hpp:13-26), a rejected call has launched nothing.  The types live in
 // namespace q4k_b200::shim so that the header can be compiled next to the reference's own; a
@@ -185,6 +186,50 @@ inline q4k_decode_desc to_abi(DecodeMmvDesc const& d) {
   return detail::lift(q4k_decode_mmv_ranges(abi, static_cast<std::uint32_t>(desc.ranges.size()), scratch.workspace.data(),
                                             scratch.workspace.size(), scratch.failure, stream.native),
                       "decode_mmv_ranges");
+}
+
+// ---- compiler/quantization/q4k.hpp ---------------------------------------------------------------
+
+enum class FitStatus : std::uint8_t {
+  Ok = Q4K_FIT_OK,
+  Nonfinite = Q4K_FIT_NONFINITE,        // CompilerErrorCode::Nonfinite
+  RangeExceeded = Q4K_FIT_RANGE,        // the rest: CompilerErrorCode::Unrepresentable
+  FitReciprocal = Q4K_FIT_RECIPROCAL,
+  CompressReciprocal = Q4K_FIT_COMPRESS,
+  HalfOverflow = Q4K_FIT_HALF,
+};
+
+// quantize_q4k_block over weights.size() / 256 consecutive blocks; all spans are device memory.
+// codes: 256 levels per block, metadata: 16 bytes per block, status: one FitStatus per block (may be
+// empty), failure: one int set to 1 when any block is refused.  The host loop of the reference stops
+// at the first refused block; here every block is attempted and that block is the lowest index
+// with a non-zero status.
+[[nodiscard]] inline std::expected<void, Error> quantize_q4k_blocks(std::span<float const> weights,
+                                                                    std::span<std::int8_t> codes,
+                                                                    std::span<std::uint8_t> metadata,
+                                                                    std::span<std::uint8_t> status, std::span<int> failure,
+                                                                    Stream const& stream) {
+  std::uint64_t const blocks = weights.size() / 256;
+  if (weights.size() % 256 != 0 || codes.size() != weights.size() || metadata.size() != blocks * 16 ||
+      (!status.empty() && status.size() != blocks) || failure.size() != 1)
+    return std::unexpected(Error{ErrorCode::InvalidArgument, 0, "q4k.fit", "invalid geometry"});
+  return detail::lift(q4k_fit_blocks(weights.data(), Q4K_FIT_FP32, blocks, codes.data(), metadata.data(),
+                                     status.empty() ? nullptr : status.data(), failure.data(), stream.native),
+                      "q4k.fit");
+}
+
+// The same from row-major [n][k] weights (fp32, or bf16 bits) straight into a split-tile weight:
+// the fitter followed by format::pack_cuda_v0.  `weight` describes the destination spans.
+[[nodiscard]] inline std::expected<void, Error> quantize_q4k_weight(void const* weights, bool bf16, PrefillWeight const& weight,
+                                                                    std::span<std::uint8_t> status, std::span<int> failure,
+                                                                    Stream const& stream) {
+  if (failure.size() != 1 || (!status.empty() && status.size() != std::uint64_t(weight.n) * (weight.k / 256)))
+    return std::unexpected(Error{ErrorCode::InvalidArgument, 0, "q4k.fit", "invalid geometry"});
+  return detail::lift(q4k_fit_weight(weights, bf16 ? Q4K_FIT_BF16 : Q4K_FIT_FP32, weight.n, weight.k,
+                                     static_cast<std::uint8_t*>(const_cast<void*>(weight.codes)), weight.codes_bytes,
+                                     static_cast<std::uint8_t*>(const_cast<void*>(weight.scales)), weight.scales_bytes,
+                                     status.empty() ? nullptr : status.data(), failure.data(), stream.native),
+                      "q4k.fit");
 }
 
 }  // namespace q4k_b200::shim

@@ -29,6 +29,12 @@ int main() {
   std::vector<DecodeMmvDesc> one(1);
   auto r5 = launch_decode_mmv_ranges(DecodeMmvRangeDesc{one}, DecodeScratch{}, Stream{});
   expect(!r5 && r5.error().detail == "two or three ranges", "ranges count");
+  // fitter: span sizes are checked in the shim, geometry in the library, both before any CUDA call
+  std::vector<int> flag(1);
+  auto r6 = quantize_q4k_blocks(std::span<float const>(static_cast<float const*>(nullptr), 300), {}, {}, {}, flag, Stream{});
+  expect(!r6 && r6.error().operation == "q4k.fit" && r6.error().detail == "invalid geometry", "fit span sizes");
+  auto r7 = quantize_q4k_weight(nullptr, true, PrefillWeight{}, {}, flag, Stream{});
+  expect(!r7 && r7.error().code == ErrorCode::InvalidArgument, "fit rejects empty weight");
   std::printf(fails ? "shim check failed\n" : "shim check ok\n");
   return fails;
 }
