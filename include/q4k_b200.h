@@ -271,6 +271,20 @@ int q4k_repack_blocks144(const uint8_t* blocks, uint64_t blocks_bytes, uint32_t 
                          uint8_t* out_codes, uint64_t out_codes_bytes, uint8_t* out_scales,
                          uint64_t out_scales_bytes, void* stream);
 
+/* format::validate_cuda_v0 for this layout (src/format/unpack.cpp:89-226) on a RESIDENT weight: rows
+ * n..padded_n-1 hold zero codes and zero metadata, every live super-block's fp16 d and dmin are
+ * non-negative and finite.  (Q4_K has no forbidden code value; k is a multiple of 256, so there are
+ * no padded columns.)  verdict: two 64-bit words in device memory, written on `stream`:
+ * verdict[0] = Q4K_VALID, or which rule the first offence in the reference's scan order breaks;
+ * verdict[1] = its byte offset inside the codes span (Q4K_INVALID_CODES_PADDING) or the scales span
+ * (the other two) -- the `offset` the reference's FormatError carries when the spans' file offsets
+ * are given as zero. */
+#define Q4K_VALID 0
+#define Q4K_INVALID_CODES_PADDING 1  /* "Q4 padded coordinates must encode zero" */
+#define Q4K_INVALID_SCALES_PADDING 2 /* "padded Q4_K metadata must be zero" */
+#define Q4K_INVALID_SCALE 3          /* "Q4_K superblock scales must be nonnegative finite FP16" */
+int q4k_validate_weight(const q4k_weight* weight, uint64_t* verdict, void* stream);
+
 /* Q4_K fitter on the device: compiler::quantize_q4k_block (src/compiler/quantization/q4k.cpp:186-278)
  * over every 256 consecutive weights, bit for bit (codes and the 16 metadata bytes).  The reference
  * runs it on the host, one block after another (quantize_fp32, src/compiler/quantization/quantizer.cpp:173-182).

@@ -67,6 +67,24 @@ int ref_validate_q4k(std::uint64_t n, std::uint64_t k, std::uint8_t const* codes
   return st ? 0 : 1;
 }
 
+// The same with the offence located: 0 admissible; 1 "quantized.codes.padding", 2 "quantized.scales.padding",
+// 3 "quantized.scales" (9 anything else); *offset = the error's byte offset inside its span.
+int ref_validate_q4k_where(std::uint64_t n, std::uint64_t k, std::uint8_t const* codes,
+                           std::uint64_t codes_bytes, std::uint8_t const* scales,
+                           std::uint64_t scales_bytes, std::uint64_t* offset) {
+  auto st = format::validate_cuda_v0(
+      format::LogicalQuantizerId::Q4KCandidateV2, format::PhysicalLayoutId::CudaQ4KCandidateV2, n, k,
+      {reinterpret_cast<std::byte const*>(codes), codes_bytes},
+      {reinterpret_cast<std::byte const*>(scales), scales_bytes});
+  *offset = 0;
+  if (st) return 0;
+  *offset = st.error().offset;
+  if (st.error().field == "quantized.codes.padding") return 1;
+  if (st.error().field == "quantized.scales.padding") return 2;
+  if (st.error().field == "quantized.scales") return 3;
+  return 9;
+}
+
 // format::unpack_cuda_v0 (src/format/unpack.cpp:262-380).
 int ref_unpack_q4k(std::uint64_t n, std::uint64_t k, std::uint8_t const* codes,
                    std::uint64_t codes_bytes, std::uint8_t const* scales,

@@ -696,6 +696,18 @@ int q4k_repack_blocks144(const uint8_t* blocks, uint64_t blocks_bytes, uint32_t 
   return Q4K_OK;
 }
 
+int q4k_validate_weight(const q4k_weight* weight, uint64_t* verdict, void* stream) {
+  if (int st = valid_weight(weight, "q4k.validate")) return st;
+  Region regions[3] = {{weight->codes, weight->codes_bytes, 16, "codes"},
+                       {weight->scales, weight->scales_bytes, 16, "scales"},
+                       {verdict, 16, 8, "verdict"}};
+  if (int st = check_distinct(regions, 3, false)) return st;
+  Q4K_CUDA(q4k::launch_validate_weight(static_cast<const uint8_t*>(weight->codes), static_cast<const uint8_t*>(weight->scales),
+                                       weight->n, weight->k, verdict, static_cast<cudaStream_t>(stream)),
+           "q4k.validate");
+  return Q4K_OK;
+}
+
 int q4k_fit_blocks(const void* weights, uint32_t weights_dtype, uint64_t blocks, int8_t* codes, uint8_t* metadata,
                    uint8_t* block_status, int* failure, void* stream) {
   if (!blocks || blocks > 0xffffffffull || weights_dtype > Q4K_FIT_BF16 || !failure)

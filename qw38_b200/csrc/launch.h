@@ -142,6 +142,10 @@ cudaError_t launch_fit_q4k(const void* weights, bool bf16, uint32_t rows, uint32
                            uint8_t* meta, uint8_t* status, int* failure, cudaStream_t stream);
 
 // repack.cu
+// verdict (device, two 64-bit words): {0, 0} admissible; else {1 padded code byte | 2 padded metadata byte |
+// 3 super-block scale, byte offset of the first offence within the codes (kind 1) or scales span}.
+cudaError_t launch_validate_weight(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, uint64_t* verdict,
+                                   cudaStream_t stream);
 cudaError_t launch_repack_blocks144(const uint8_t* blocks, uint32_t n, uint32_t k, uint8_t* codes,
                                     uint8_t* meta, cudaStream_t stream);
 

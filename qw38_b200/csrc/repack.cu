@@ -32,7 +32,65 @@ __global__ void __launch_bounds__(128) repack_blocks144_kernel(const uint8_t* __
   if (j < 16) meta[tr * 16 + j] = mv;
 }
 
+// Admissibility of a resident split-tile weight, the Q4_K rows of format::validate_cuda_v0
+// (src/format/unpack.cpp:156-226): a padded row (row >= n) holds zero codes and zero metadata; a live
+// row's fp16 d and dmin are non-negative and finite.  The reference walks tile rows in index order,
+// codes before metadata, and reports the first offence; here every tile row is checked by one thread
+// and the smallest key (tile_row, stage, byte) wins an atomic minimum, which is the same offence.
+// stage: 0 padded code byte, 1 padded metadata byte, 2 super-block scale.
+__global__ void __launch_bounds__(256) validate_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ meta,
+                                                       uint32_t n, uint32_t tiles_k, uint64_t tile_rows,
+                                                       unsigned long long* __restrict__ key) {
+  uint64_t const tr = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (tr >= tile_rows) return;
+  uint32_t const row = uint32_t((tr >> 3) / tiles_k) * 8 + uint32_t(tr & 7);
+  uint4 const m = reinterpret_cast<const uint4*>(meta)[tr];
+  unsigned long long found = ~0ull;
+  if (row >= n) {
+    uint32_t const mw[4] = {m.x, m.y, m.z, m.w};
+    for (int w = 3; w >= 0; --w)
+      if (mw[w]) found = (tr << 10) | (1u << 8) | uint32_t(4 * w + (__ffs(mw[w]) - 1) / 8);
+    const uint4* c = reinterpret_cast<const uint4*>(codes) + tr * 8;
+    for (int q = 7; q >= 0; --q) {
+      uint4 const v = c[q];
+      uint32_t const cw[4] = {v.x, v.y, v.z, v.w};
+      for (int w = 3; w >= 0; --w)
+        if (cw[w]) found = (tr << 10) | uint32_t(16 * q + 4 * w + (__ffs(cw[w]) - 1) / 8);
+    }
+  } else {
+    uint32_t const d = m.x & 0xffffu, dmin = m.x >> 16;
+    if ((dmin & 0x8000u) || (dmin & 0x7c00u) == 0x7c00u) found = (tr << 10) | (2u << 8) | 2u;
+    if ((d & 0x8000u) || (d & 0x7c00u) == 0x7c00u) found = (tr << 10) | (2u << 8) | 0u;
+  }
+  if (found != ~0ull) atomicMin(key, found);
+}
+
+// verdict[1] holds the winning key on entry; rewrites verdict as {kind, byte offset in its span}.
+__global__ void validate_verdict_kernel(unsigned long long* verdict) {
+  unsigned long long const key = verdict[1];
+  if (key == ~0ull) {
+    verdict[0] = 0;
+    verdict[1] = 0;
+    return;
+  }
+  unsigned long long const tr = key >> 10, stage = (key >> 8) & 3u, byte = key & 0xffu;
+  verdict[0] = stage + 1;
+  verdict[1] = stage == 0 ? tr * 128 + byte : tr * 16 + byte;
+}
+
 }  // namespace
+
+cudaError_t launch_validate_weight(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, uint64_t* verdict,
+                                   cudaStream_t stream) {
+  uint32_t const tiles_k = k / 256;
+  uint64_t const tile_rows = uint64_t((n + 7) / 8 * 8) * tiles_k;
+  auto* v = reinterpret_cast<unsigned long long*>(verdict);
+  cudaError_t st = cudaMemsetAsync(v, 0xff, 16, stream);
+  if (st != cudaSuccess) return st;
+  validate_kernel<<<unsigned((tile_rows + 255) / 256), 256, 0, stream>>>(codes, meta, n, tiles_k, tile_rows, v + 1);
+  validate_verdict_kernel<<<1, 1, 0, stream>>>(v);
+  return cudaGetLastError();
+}
 
 cudaError_t launch_repack_blocks144(const uint8_t* blocks, uint32_t n, uint32_t k, uint8_t* codes,
                                     uint8_t* meta, cudaStream_t stream) {

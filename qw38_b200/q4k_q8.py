@@ -340,6 +340,23 @@ def export_q8_1(x: Q8Input, stream=None) -> torch.Tensor:
     return rec
 
 
+VALIDATE_ERRORS = {
+    1: ("quantized.codes.padding", "Q4 padded coordinates must encode zero"),
+    2: ("quantized.scales.padding", "padded Q4_K metadata must be zero"),
+    3: ("quantized.scales", "Q4_K superblock scales must be nonnegative finite FP16"),
+}
+
+
+def validate_weight(weight: PrefillWeight, stream=None):
+    """format::validate_cuda_v0 (src/format/unpack.cpp:89-226) on a resident weight.  Returns
+    (0, 0) when admissible, else (kind, byte offset of the first offence in the reference's scan
+    order); VALIDATE_ERRORS[kind] is the reference's (field, detail).  Synchronises."""
+    verdict = torch.empty(2, dtype=torch.int64, device=weight.codes.device)
+    _check(L.load().q4k_validate_weight(C.byref(weight.c_struct()), _ptr(verdict), _stream(stream)))
+    kind, offset = verdict.cpu().tolist()
+    return int(kind), int(offset)
+
+
 FIT_ERRORS = {
     1: "Q4_K input is nonfinite",
     2: "Q4_K fitting range exceeded",

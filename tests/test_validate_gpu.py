@@ -1,0 +1,106 @@
+"""GPU tests of q4k_validate_weight: the Q4_K rows of format::validate_cuda_v0
+(src/format/unpack.cpp:156-226) on a resident weight.  Offences are planted at known bytes; the
+verdict must name the first one in the reference's scan order (tile rows ascending, codes before
+metadata, d before dmin) -- checked analytically and, where the reference's host code was built
+on this machine, against it."""
+import ctypes as C
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle as orc
+from qw38_b200 import synth
+from qw38_b200.q4k_q8 import PrefillWeight, VALIDATE_ERRORS, quantize_q4k_weight, validate_weight
+
+pytestmark = pytest.mark.gpu
+
+
+def host_weight(n, k, seed):
+    codes, meta = synth.logical_q4k(n, k, seed=seed)
+    return synth.split_tiles(codes, meta)
+
+
+def reference_verdict(n, k, hc, hs):
+    ref = orc.ref()
+    if ref is None or not hasattr(ref, "ref_validate_q4k_where"):
+        return None
+    off = C.c_uint64(0)
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
+    kind = ref.ref_validate_q4k_where(C.c_uint64(n), C.c_uint64(k), vp(hc), C.c_uint64(hc.size), vp(hs), C.c_uint64(hs.size),
+                                      C.byref(off))
+    return kind, off.value
+
+
+def check(n, k, hc, hs, want):
+    got = validate_weight(PrefillWeight.from_host(hc, hs, n, k))
+    assert got == want
+    ref = reference_verdict(n, k, hc, hs)
+    if ref is not None:
+        assert ref == want
+
+
+def tile_row(row, kb, tiles_k):
+    return ((row // 8) * tiles_k + kb) * 8 + row % 8
+
+
+@pytest.mark.parametrize("n,k", [(137, 512), (64, 1024), (5, 256)])
+def test_packed_weights_are_admissible(n, k):
+    hc, hs = host_weight(n, k, 3)
+    check(n, k, hc, hs, (0, 0))
+    assert sorted(VALIDATE_ERRORS) == [1, 2, 3]
+
+
+def test_fitted_weights_are_admissible():
+    w = torch.randn(37, 768, device="cuda") * 0.1
+    assert validate_weight(quantize_q4k_weight(w)) == (0, 0)
+
+
+def test_each_rule_and_its_offset():
+    n, k, tiles_k = 137, 512, 2
+    hc, hs = host_weight(n, k, 4)
+    # a code nibble in a padded row
+    c = hc.copy(); tr = tile_row(140, 1, tiles_k); c[tr * 128 + 77] = 0x30
+    check(n, k, c, hs, (1, tr * 128 + 77))
+    # a metadata byte in a padded row
+    s = hs.copy(); tr = tile_row(143, 0, tiles_k); s[tr * 16 + 9] = 1
+    check(n, k, hc, s, (2, tr * 16 + 9))
+    # negative d, infinite dmin, NaN d on live rows
+    s = hs.copy(); tr = tile_row(20, 1, tiles_k); s[tr * 16 + 1] |= 0x80
+    check(n, k, hc, s, (3, tr * 16))
+    s = hs.copy(); tr = tile_row(136, 0, tiles_k); s[tr * 16 + 2] = 0x00; s[tr * 16 + 3] = 0x7C
+    check(n, k, hc, s, (3, tr * 16 + 2))
+    s = hs.copy(); tr = tile_row(0, 0, tiles_k); s[tr * 16 + 0] = 0x01; s[tr * 16 + 1] = 0x7E
+    check(n, k, hc, s, (3, tr * 16))
+    # fp16 subnormal and zero scales are admissible
+    s = hs.copy(); tr = tile_row(9, 1, tiles_k); s[tr * 16: tr * 16 + 4] = [1, 0, 0, 0]
+    check(n, k, hc, s, (0, 0))
+
+
+def test_first_offence_in_scan_order_wins():
+    n, k, tiles_k = 137, 512, 2
+    hc, hs = host_weight(n, k, 5)
+    c, s = hc.copy(), hs.copy()
+    late = tile_row(142, 1, tiles_k)
+    c[late * 128 + 3] = 0x01                      # padded code, late tile row
+    early = tile_row(139, 1, tiles_k)
+    s[early * 16 + 15] = 0xFF                     # padded metadata, earlier tile row
+    check(n, k, c, s, (2, early * 16 + 15))
+    c[early * 128 + 127] = 0xF0                   # same tile row: codes are scanned before metadata
+    check(n, k, c, s, (1, early * 128 + 127))
+    c[early * 128 + 5] = 0x0A                     # lower byte of the same row
+    check(n, k, c, s, (1, early * 128 + 5))
+    live = tile_row(77, 0, tiles_k)
+    s[live * 16 + 3] |= 0x80                      # dmin negative in a far earlier tile row
+    check(n, k, c, s, (3, live * 16 + 2))
+    s[live * 16 + 1] |= 0x80                      # d of the same block is read first
+    check(n, k, c, s, (3, live * 16))
+
+
+def test_large_weight_with_one_planted_offence():
+    n, k = 5120, 5120
+    hc, hs = host_weight(n, k, 6)
+    check(n, k, hc, hs, (0, 0))
+    s = hs.copy(); tr = tile_row(4097, 13, 20); s[tr * 16 + 3] = 0xFC
+    got = validate_weight(PrefillWeight.from_host(hc, s, n, k))
+    assert got == (3, tr * 16 + 2)
