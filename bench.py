@@ -572,7 +572,27 @@ def main():
         t = e0.elapsed_time(e1) / 5
         fitter = {"workload": f"fit bf16 {n}x{k} -> split-tile Q4_K", "ms": round(t, 3), "kernel": "fit_q4k_kernel",
                   "Mblocks_per_s": round(n * k / 256 / (t * 1e-3) / 1e6, 1)}
+        # and back: resident split tiles -> bf16 [n, k] (the operand of the reference's unpack -> cuBLAS prefill path)
+        import ctypes
+        from qw38_b200 import _lib as L
+        pw = quantize_q4k_weight(wf, check=False)
         del wf
+        deq = torch.empty((n, k), dtype=torch.bfloat16, device=dev)
+        ws = pw.c_struct()
+        lib = L.load()
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                lib.q4k_dequantize_bf16(ctypes.byref(ws), ctypes.c_void_p(deq.data_ptr()), deq.numel(), ctypes.c_void_p(stream.cuda_stream))
+            e0.record(stream)
+            for _ in range(20):
+                lib.q4k_dequantize_bf16(ctypes.byref(ws), ctypes.c_void_p(deq.data_ptr()), deq.numel(), ctypes.c_void_p(stream.cuda_stream))
+            e1.record(stream)
+        stream.synchronize()
+        t = e0.elapsed_time(e1) / 20
+        nbytes = pw.nbytes() + deq.numel() * 2
+        fitter["dequantize_bf16"] = {"ms": round(t, 4), "kernel": "dequantize_bf16_kernel", "GBps": round(nbytes / (t * 1e-3) / 1e9, 1),
+                                     "frac_of_hbm_peak": round(nbytes / (t * 1e-3) / 1e9 / hbm_peak, 4), "bytes": nbytes}
+        del pw, deq
 
     if rank == 0:
         dom = max(per_kernel, key=lambda kk: per_kernel[kk]["ms"])

@@ -285,6 +285,13 @@ int q4k_repack_blocks144(const uint8_t* blocks, uint64_t blocks_bytes, uint32_t 
 #define Q4K_INVALID_SCALE 3          /* "Q4_K superblock scales must be nonnegative finite FP16" */
 int q4k_validate_weight(const q4k_weight* weight, uint64_t* verdict, void* stream);
 
+/* compiler::dequantize_to_bf16 (src/compiler/quantization/reference.cpp:141-166) from the resident
+ * split-tile weight: output bf16 bits [n][k] row-major (k % 256 == 0, output_len = n*k), each value
+ * bf16_rne((d*sc)*q - dmin*mn) with separately rounded fp32 operations -- the operand the reference's
+ * BF16 unpack -> cuBLAS prefill path multiplies with (cuda/prefill.cu:329-335), and the weights its
+ * reference GEMV sees. */
+int q4k_dequantize_bf16(const q4k_weight* weight, uint16_t* output, uint64_t output_len, void* stream);
+
 /* Q4_K fitter on the device: compiler::quantize_q4k_block (src/compiler/quantization/q4k.cpp:186-278)
  * over every 256 consecutive weights, bit for bit (codes and the 16 metadata bytes).  The reference
  * runs it on the host, one block after another (quantize_fp32, src/compiler/quantization/quantizer.cpp:173-182).

@@ -143,6 +143,30 @@ def logical_to_blocks144(codes: np.ndarray, meta: np.ndarray) -> np.ndarray:
     return out
 
 
+def dequantize_bf16(codes: np.ndarray, meta: np.ndarray) -> np.ndarray:
+    """Logical codes [n, k] (0..15) + metadata [n, k/256, 16] -> bf16 bits [n, k]:
+    bf16_rne((d * sc) * q - dmin * mn), every operation rounded to fp32, as
+    compiler::dequantize_to_bf16 (src/compiler/quantization/reference.cpp:141-166).  numpy float32
+    arithmetic rounds each operation separately, which is what the reference's host build does."""
+    n, k = codes.shape
+    f32 = np.float32
+    meta = np.ascontiguousarray(meta).reshape(n, k // 256, 16)
+    d = meta[..., 0:2].copy().view(np.float16).astype(f32)[..., 0]
+    dmin = meta[..., 2:4].copy().view(np.float16).astype(f32)[..., 0]
+    p = meta[..., 4:].astype(np.uint32)
+    sc = np.empty((n, k // 256, 8), dtype=np.uint32)
+    mn = np.empty_like(sc)
+    sc[..., :4], mn[..., :4] = p[..., 0:4] & 63, p[..., 4:8] & 63
+    sc[..., 4:] = (p[..., 8:12] & 15) | ((p[..., 0:4] >> 6) << 4)
+    mn[..., 4:] = (p[..., 8:12] >> 4) | ((p[..., 4:8] >> 6) << 4)
+    step = (d[..., None] * sc.astype(f32)).astype(f32)
+    offset = (dmin[..., None] * mn.astype(f32)).astype(f32)
+    q = codes.reshape(n, k // 256, 8, 32).astype(f32)
+    w = ((step[..., None] * q).astype(f32) - offset[..., None]).astype(f32).reshape(n, k)
+    bits = w.view(np.uint32).astype(np.uint64)
+    return ((bits + 0x7FFF + ((bits >> 16) & 1)) >> 16).astype(np.uint16)
+
+
 def dots(wcodes: np.ndarray, n: int, padded_k: int, z: np.ndarray) -> np.ndarray:
     """Exact int32 K32 partial dots [m, n, padded_k/32]."""
     m = z.shape[0]

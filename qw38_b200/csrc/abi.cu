@@ -708,6 +708,20 @@ int q4k_validate_weight(const q4k_weight* weight, uint64_t* verdict, void* strea
   return Q4K_OK;
 }
 
+int q4k_dequantize_bf16(const q4k_weight* weight, uint16_t* output, uint64_t output_len, void* stream) {
+  if (int st = valid_weight(weight, "q4k.dequantize")) return st;
+  if (weight->k % 256 != 0 || output_len != uint64_t(weight->n) * weight->k)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q4k.dequantize: invalid geometry");
+  Region regions[3] = {{weight->codes, weight->codes_bytes, 16, "codes"},
+                       {weight->scales, weight->scales_bytes, 16, "scales"},
+                       {output, output_len * 2, 16, "output"}};
+  if (int st = check_distinct(regions, 3, false)) return st;
+  Q4K_CUDA(q4k::launch_dequantize_bf16(static_cast<const uint8_t*>(weight->codes), static_cast<const uint8_t*>(weight->scales),
+                                       weight->n, weight->k, output, static_cast<cudaStream_t>(stream)),
+           "q4k.dequantize");
+  return Q4K_OK;
+}
+
 int q4k_fit_blocks(const void* weights, uint32_t weights_dtype, uint64_t blocks, int8_t* codes, uint8_t* metadata,
                    uint8_t* block_status, int* failure, void* stream) {
   if (!blocks || blocks > 0xffffffffull || weights_dtype > Q4K_FIT_BF16 || !failure)

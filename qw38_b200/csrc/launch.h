@@ -142,6 +142,9 @@ cudaError_t launch_fit_q4k(const void* weights, bool bf16, uint32_t rows, uint32
                            uint8_t* meta, uint8_t* status, int* failure, cudaStream_t stream);
 
 // repack.cu
+// bf16 weights [n][k] (k % 256 == 0) from split tiles: bf16_rne((d*sc)*q - dmin*mn), each operation rounded.
+cudaError_t launch_dequantize_bf16(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, uint16_t* out,
+                                   cudaStream_t stream);
 // verdict (device, two 64-bit words): {0, 0} admissible; else {1 padded code byte | 2 padded metadata byte |
 // 3 super-block scale, byte offset of the first offence within the codes (kind 1) or scales span}.
 cudaError_t launch_validate_weight(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, uint64_t* verdict,

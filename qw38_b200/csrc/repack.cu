@@ -6,6 +6,8 @@
 // (third_party/llama.cpp-q4k/reference.hpp:244-248,253-275).  A tile row keeps the 16
 // metadata bytes as they are and stores element 2j in the low and 2j+1 in the high nibble
 // of code byte j (src/format/pack.cpp:201-222).  Rows n..ceil8(n)-1 are written as zeros.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 #include "launch.h"
 
@@ -65,6 +67,52 @@ __global__ void __launch_bounds__(256) validate_kernel(const uint8_t* __restrict
   if (found != ~0ull) atomicMin(key, found);
 }
 
+// Split tiles -> bf16 weights [n][k] row-major, the values of compiler::dequantize_to_bf16
+// (src/compiler/quantization/reference.cpp:141-166): w = bf16_rne((d * sc) * q - dmin * mn) with three
+// separately rounded fp32 operations.  One thread turns one code word (8 weights) into one 16-byte
+// store.  A block of eight warps takes one group of eight rows and kDeqTiles consecutive K tiles
+// (a contiguous run of the tiled input); warp r owns row r, so that it writes kDeqTiles * 512
+// contiguous bytes of that row, with all its loads issued before the first store.
+constexpr int kDeqTiles = 4;
+__global__ void __launch_bounds__(256) dequantize_bf16_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ meta,
+                                                              uint32_t n, uint32_t tiles_k, uint32_t chunks_k,
+                                                              uint16_t* __restrict__ out) {
+  uint32_t const group = blockIdx.x / chunks_k, kb0 = (blockIdx.x % chunks_k) * kDeqTiles;
+  uint32_t const r = threadIdx.x >> 5, c = threadIdx.x & 31, g = c >> 2;
+  uint32_t const row = group * 8 + r;
+  if (row >= n) return;
+  uint4 m[kDeqTiles];
+  uint32_t w[kDeqTiles];
+#pragma unroll
+  for (int t = 0; t < kDeqTiles; ++t) {
+    if (kb0 + t < tiles_k) {
+      uint64_t const tr = (uint64_t(group) * tiles_k + kb0 + t) * 8 + r;
+      m[t] = __ldg(reinterpret_cast<const uint4*>(meta) + tr);
+      w[t] = __ldg(reinterpret_cast<const uint32_t*>(codes) + tr * 32 + c);
+    }
+  }
+#pragma unroll
+  for (int t = 0; t < kDeqTiles; ++t) {
+    if (kb0 + t >= tiles_k) break;
+    ScaleMinWords const sm = decode_scale_min(m[t].y, m[t].z, m[t].w);
+    uint32_t const sc = byte_of(g < 4 ? sm.sc_lo : sm.sc_hi, g & 3), mn = byte_of(g < 4 ? sm.mn_lo : sm.mn_hi, g & 3);
+    float const step = __fmul_rn(fp16_bits_to_f32(m[t].x & 0xffffu), float(sc));
+    float const offset = __fmul_rn(fp16_bits_to_f32(m[t].x >> 16), float(mn));
+    uint32_t packed[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      // level -> float through the 2^23 bias (exact, and on the full-rate pipes); the pair is rounded
+      // to bf16 by one conversion instruction (round to nearest even; values are finite)
+      float const lo = __fsub_rn(__uint_as_float(0x4b000000u | ((w[t] >> (8 * i)) & 15u)), 8388608.f);
+      float const hi = __fsub_rn(__uint_as_float(0x4b000000u | ((w[t] >> (8 * i + 4)) & 15u)), 8388608.f);
+      __nv_bfloat162 const pair = __floats2bfloat162_rn(__fsub_rn(__fmul_rn(step, lo), offset), __fsub_rn(__fmul_rn(step, hi), offset));
+      packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
+    }
+    uint64_t const at = (uint64_t(row) * tiles_k + kb0 + t) * 256 + 8 * c;
+    __stcs(reinterpret_cast<uint4*>(out + at), make_uint4(packed[0], packed[1], packed[2], packed[3]));
+  }
+}
+
 // verdict[1] holds the winning key on entry; rewrites verdict as {kind, byte offset in its span}.
 __global__ void validate_verdict_kernel(unsigned long long* verdict) {
   unsigned long long const key = verdict[1];
@@ -89,6 +137,15 @@ cudaError_t launch_validate_weight(const uint8_t* codes, const uint8_t* meta, ui
   if (st != cudaSuccess) return st;
   validate_kernel<<<unsigned((tile_rows + 255) / 256), 256, 0, stream>>>(codes, meta, n, tiles_k, tile_rows, v + 1);
   validate_verdict_kernel<<<1, 1, 0, stream>>>(v);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_dequantize_bf16(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, uint16_t* out,
+                                   cudaStream_t stream) {
+  uint32_t const tiles_k = k / 256, chunks_k = (tiles_k + kDeqTiles - 1) / kDeqTiles;
+  uint64_t const blocks = uint64_t((n + 7) / 8) * chunks_k;
+  if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+  dequantize_bf16_kernel<<<unsigned(blocks), 256, 0, stream>>>(codes, meta, n, tiles_k, chunks_k, out);
   return cudaGetLastError();
 }
 

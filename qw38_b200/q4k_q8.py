@@ -357,6 +357,14 @@ def validate_weight(weight: PrefillWeight, stream=None):
     return int(kind), int(offset)
 
 
+def dequantize_bf16(weight: PrefillWeight, stream=None) -> torch.Tensor:
+    """compiler::dequantize_to_bf16 (src/compiler/quantization/reference.cpp:141-166) from the resident
+    weight: bfloat16 [n, k]."""
+    out = torch.empty((weight.n, weight.k), dtype=torch.bfloat16, device=weight.codes.device)
+    _check(L.load().q4k_dequantize_bf16(C.byref(weight.c_struct()), _ptr(out), out.numel(), _stream(stream)))
+    return out
+
+
 FIT_ERRORS = {
     1: "Q4_K input is nonfinite",
     2: "Q4_K fitting range exceeded",

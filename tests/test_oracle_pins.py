@@ -119,6 +119,11 @@ def test_dequant_and_bf16_policy_gemv_match_reference(golden):
                 assert (want.astype(np.float32).view(np.uint32) == deq[i, b * 256 + g * 32:b * 256 + (g + 1) * 32].view(np.uint32)).all()
 
 
+def test_bf16_dequantiser_matches_reference(golden):
+    got = orc.dequantize_bf16(golden["a_codes"], golden["a_meta"])
+    assert (got == golden["a_dequant_bf16"]).all()
+
+
 def reference_test_input(m: int, k: int) -> np.ndarray:
     """bf16 activations of tests/q4k_q8_test.cpp:69-77."""
     r = np.arange(m)[:, None]

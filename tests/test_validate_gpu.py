@@ -104,3 +104,47 @@ def test_large_weight_with_one_planted_offence():
     s = hs.copy(); tr = tile_row(4097, 13, 20); s[tr * 16 + 3] = 0xFC
     got = validate_weight(PrefillWeight.from_host(hc, s, n, k))
     assert got == (3, tr * 16 + 2)
+
+
+# ---- q4k_dequantize_bf16: compiler::dequantize_to_bf16 from the resident weight ---------------------
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def test_dequantise_matches_reference_vectors(golden):
+    from qw38_b200.q4k_q8 import dequantize_bf16
+    w = PrefillWeight.from_host(golden["a_packed_codes"], golden["a_packed_scales"], 137, 512)
+    assert np.array_equal(bf16_bits(dequantize_bf16(w)), golden["a_dequant_bf16"])
+
+
+@pytest.mark.parametrize("n,k", [(300, 1280), (8, 256), (1021, 5120)])
+def test_dequantise_matches_cpu_statement(n, k):
+    from qw38_b200.q4k_q8 import dequantize_bf16
+    codes, meta = synth.logical_q4k(n, k, seed=n)
+    hc, hs = synth.split_tiles(codes, meta)
+    got = bf16_bits(dequantize_bf16(PrefillWeight.from_host(hc, hs, n, k)))
+    assert np.array_equal(got, orc.dequantize_bf16(codes[:, :k], meta))
+
+
+def test_fit_then_dequantise_stays_close_to_the_weights():
+    from qw38_b200.q4k_q8 import dequantize_bf16
+    torch.manual_seed(3)
+    w = torch.randn(64, 2048, device="cuda") * 0.05
+    back = dequantize_bf16(quantize_q4k_weight(w)).float()
+    err = (back - w).abs().reshape(64, -1, 32)
+    span = (w.reshape(64, -1, 32).amax(dim=2) - w.reshape(64, -1, 32).amin(dim=2).clamp(max=0)).unsqueeze(2)
+    # in units of a group's step (range / 15): the weighted fit may clip an outlier by most of a step,
+    # the typical error is a quarter of one (the reference's host fitter gives 0.83 and 0.26 here)
+    ratio = err / (span / 15)
+    assert float(ratio.max()) < 1.25 and float((ratio ** 2).mean().sqrt()) < 0.35
+
+
+def test_dequantise_rejects_wrong_output_length():
+    import ctypes
+    from qw38_b200 import _lib as L
+    codes, meta = synth.logical_q4k(16, 256, seed=1)
+    w = PrefillWeight.from_host(*synth.split_tiles(codes, meta), 16, 256)
+    out = torch.zeros(16 * 256 + 8, dtype=torch.bfloat16, device="cuda")
+    st = L.load().q4k_dequantize_bf16(ctypes.byref(w.c_struct()), ctypes.c_void_p(out.data_ptr()), out.numel(), None)
+    assert st == L.ERR_INVALID_ARGUMENT and not out.any()
