@@ -45,10 +45,51 @@ __device__ __forceinline__ int nearest(float v) {
 }
 __device__ __forceinline__ int level(float v) { return min(15, max(0, nearest(v))); }
 
+// The same rounding kept as a float: (v + 1.5 * 2^23) - 1.5 * 2^23 is v rounded to the nearest even integer
+// whenever |v| < 2^22, and clamping that to [0, 15] gives float(level(v)) without a conversion
+// instruction.  Only used where the caller has bounded |v|.
+__device__ __forceinline__ float level_bounded(float v) {
+  return fminf(fmaxf(sub(add(v, 12582912.f), 12582912.f), 0.f), 15.f);
+}
+template <bool Bounded>
+__device__ __forceinline__ float level_f(float v) { return Bounded ? level_bounded(v) : float(level(v)); }
+
 struct GroupFit {
   float scale, the_min;  // results of the search: step and (negated) minimum
   float grid, origin;    // the levels the search settled on are level(grid * (x - origin))
 };
+
+struct Moments { float l, l2, xl; };
+
+// Weighted moments of the levels a candidate grid assigns (the middle loop of the search).
+template <bool Bounded>
+__device__ __forceinline__ Moments moments(const float* x, float average, float grid, float origin) {
+  Moments s{0.f, 0.f, 0.f};
+#pragma unroll 8
+  for (int i = 0; i < 32; ++i) {
+    float const v = x[i];
+    float const l = level_f<Bounded>(mul(grid, sub(v, origin)));
+    float const wl = mul(add(average, fabsf(v)), l);
+    s.l = add(s.l, wl);
+    s.l2 = add(s.l2, mul(wl, l));
+    s.xl = add(s.xl, mul(wl, v));
+  }
+  return s;
+}
+
+// Weighted squared error of step * level + base against the weights.
+template <bool Bounded>
+__device__ __forceinline__ float fit_error(const float* x, float average, float grid, float origin, float step, float base) {
+  float err = 0.f;
+#pragma unroll 8
+  for (int i = 0; i < 32; ++i) {
+    float const v = x[i];
+    float const l = level_f<Bounded>(mul(grid, sub(v, origin)));
+    float const diff = sub(add(mul(step, l), base), v);
+    err = add(err, mul(add(average, fabsf(v)), mul(diff, diff)));
+  }
+  return err;
+}
 
 // The search over one group (make_qkx2_quants with n=32, nmax=15, rmin=-1, rdelta=0.1, nstep=20,
 // squared error; q4k.cpp:94-172).  x points at the group's 32 weights in shared memory.
@@ -56,7 +97,7 @@ __device__ GroupFit fit_group(const float* x, float average) {
   float lo = x[0], hi = x[0];
   float sum_w = add(average, fabsf(x[0]));
   float sum_x = mul(sum_w, x[0]);
-#pragma unroll 4
+#pragma unroll 8
   for (int i = 1; i < 32; ++i) {
     float const v = x[i], w = add(average, fabsf(v));
     if (v < lo) lo = v;
@@ -64,54 +105,35 @@ __device__ GroupFit fit_group(const float* x, float average) {
     sum_w = add(sum_w, w);
     sum_x = add(sum_x, mul(w, v));
   }
+  float const x_min = lo;  // smallest weight, before the minimum is capped at zero
   if (lo > 0.f) lo = 0.f;
   GroupFit fit;
   if (hi == lo) {
     fit.scale = 0.f; fit.the_min = -lo; fit.grid = 0.f; fit.origin = lo;
     return fit;
   }
-  float const range = sub(hi, lo);
-  float grid = quo(15.f, range);
+  float grid = quo(15.f, sub(hi, lo));
   float scale = quo(1.f, grid);
-  float best = 0.f;
-#pragma unroll 4
-  for (int i = 0; i < 32; ++i) {
-    float const v = x[i];
-    float const l = float(level(mul(grid, sub(v, lo))));
-    float const diff = sub(add(mul(scale, l), lo), v);
-    best = add(best, mul(add(average, fabsf(v)), mul(diff, diff)));
-  }
+  float best = fit_error<false>(x, average, grid, lo, scale, lo);
   fit.grid = grid; fit.origin = lo;
   float floor_ = lo;  // the minimum candidates quantise against; moves when one is accepted
   for (int step = 0; step <= 20; ++step) {
     // (rmin + rdelta*step + nmax) / (max - min), with the minimum as moved so far.
     float const cand_grid = quo(add(add(-1.f, mul(0.1f, float(step))), 15.f), sub(hi, floor_));
-    float sum_l = 0.f, sum_l2 = 0.f, sum_xl = 0.f;
-#pragma unroll 4
-    for (int i = 0; i < 32; ++i) {
-      float const v = x[i];
-      float const l = float(level(mul(cand_grid, sub(v, floor_))));
-      float const wl = mul(add(average, fabsf(v)), l);
-      sum_l = add(sum_l, wl);
-      sum_l2 = add(sum_l2, mul(wl, l));
-      sum_xl = add(sum_xl, mul(wl, v));
-    }
-    float const det = sub(mul(sum_w, sum_l2), mul(sum_l, sum_l));
+    // Every grid * (x - origin) of this candidate is bounded by |grid| times the larger distance of
+    // the extreme weights from the origin (rounding is monotonic); below 2^22 the float rounding applies.
+    bool const bounded = mul(fabsf(cand_grid), fmaxf(fabsf(sub(hi, floor_)), fabsf(sub(x_min, floor_)))) < 4194304.f;
+    Moments const s = bounded ? moments<true>(x, average, cand_grid, floor_) : moments<false>(x, average, cand_grid, floor_);
+    float const det = sub(mul(sum_w, s.l2), mul(s.l, s.l));
     if (!(det > 0.f)) continue;
-    float cand_scale = quo(sub(mul(sum_w, sum_xl), mul(sum_x, sum_l)), det);
-    float cand_min = quo(sub(mul(sum_l2, sum_x), mul(sum_l, sum_xl)), det);
+    float cand_scale = quo(sub(mul(sum_w, s.xl), mul(sum_x, s.l)), det);
+    float cand_min = quo(sub(mul(s.l2, sum_x), mul(s.l, s.xl)), det);
     if (cand_min > 0.f) {
       cand_min = 0.f;
-      cand_scale = quo(sum_xl, sum_l2);
+      cand_scale = quo(s.xl, s.l2);
     }
-    float err = 0.f;
-#pragma unroll 4
-    for (int i = 0; i < 32; ++i) {
-      float const v = x[i];
-      float const l = float(level(mul(cand_grid, sub(v, floor_))));
-      float const diff = sub(add(mul(cand_scale, l), cand_min), v);
-      err = add(err, mul(add(average, fabsf(v)), mul(diff, diff)));
-    }
+    float const err = bounded ? fit_error<true>(x, average, cand_grid, floor_, cand_scale, cand_min)
+                              : fit_error<false>(x, average, cand_grid, floor_, cand_scale, cand_min);
     if (err < best) {
       best = err;
       scale = cand_scale;

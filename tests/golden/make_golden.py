@@ -109,7 +109,7 @@ def main() -> None:
 
     # --- E. Fitter corner cases and refusals (quantize_q4k_block, every block attempted). -------
     from tests.helpers import fitter_cases
-    cases = np.ascontiguousarray(fitter_cases(20240612, 103))
+    cases = np.ascontiguousarray(fitter_cases(20240612, 98))
     nb = cases.shape[0]
     e_codes = np.zeros((nb, 256), dtype=np.int8)
     e_meta = np.zeros((nb, 16), dtype=np.uint8)

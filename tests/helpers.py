@@ -60,6 +60,11 @@ def fitter_cases(seed: int, random_blocks: int) -> np.ndarray:
     add(np.round(normal(3.0)))                            # many exact ties
     add(np.tile(np.arange(16, dtype=f32), 16) - 8.0)      # exactly representable grid
     w = np.zeros(256); w[200] = 1.0; add(w)               # a single spike
+    add(-1000.0 + normal(1e-3))                           # narrow band far below zero: offset >> step
+    add(1000.0 + normal(1e-3))                            # narrow band far above zero: minimum capped at 0
+    w = normal(0.02); w[:32] = -50.0 + rng.standard_normal(32) * 1e-4; add(w)
+    add(-np.tile(np.linspace(1.0, 2.0, 32), 8))           # one-sided ramps
+    add(-np.abs(normal(1.0)) - 1e3 * np.repeat(rng.random(8), 32))
     # refusals
     add(normal(1e-38))                                    # fitting reciprocal overflow
     add(normal(2e-38) + 1e-37)                            # compression reciprocal overflow (or earlier)
