@@ -14,8 +14,8 @@
 // builds its host code with -ffp-contract=off, src/CMakeLists.txt:35-37).
 //
 // A block of 128 threads fits 16 consecutive super-blocks.  Their 4096 weights are loaded with
-// coalesced reads into shared memory at a row stride of 33 words, so that the per-thread walks
-// over "its" 32 weights are bank-conflict free.  Output is either the logical form of the
+// coalesced reads into shared memory at a row stride of 33 words, from where each thread takes
+// "its" 32 weights into registers without bank conflicts.  Output is either the logical form of the
 // reference's compiler (int8 codes [blocks][256] + 16 metadata bytes per block) or directly the
 // split-tile device layout (src/format/pack.cpp:175-222), which fuses the pack step.
 #include <cuda_fp16.h>
@@ -63,13 +63,13 @@ struct Moments { float l, l2, xl; };
 
 // Weighted moments of the levels a candidate grid assigns (the middle loop of the search).
 template <bool Bounded>
-__device__ __forceinline__ Moments moments(const float* x, float average, float grid, float origin) {
+__device__ __forceinline__ Moments moments(const float (&x)[32], const float (&w)[32], float grid, float origin) {
   Moments s{0.f, 0.f, 0.f};
-#pragma unroll 8
+#pragma unroll
   for (int i = 0; i < 32; ++i) {
     float const v = x[i];
     float const l = level_f<Bounded>(mul(grid, sub(v, origin)));
-    float const wl = mul(add(average, fabsf(v)), l);
+    float const wl = mul(w[i], l);
     s.l = add(s.l, wl);
     s.l2 = add(s.l2, mul(wl, l));
     s.xl = add(s.xl, mul(wl, v));
@@ -79,31 +79,35 @@ __device__ __forceinline__ Moments moments(const float* x, float average, float 
 
 // Weighted squared error of step * level + base against the weights.
 template <bool Bounded>
-__device__ __forceinline__ float fit_error(const float* x, float average, float grid, float origin, float step, float base) {
+__device__ __forceinline__ float fit_error(const float (&x)[32], const float (&w)[32], float grid, float origin, float step, float base) {
   float err = 0.f;
-#pragma unroll 8
+#pragma unroll
   for (int i = 0; i < 32; ++i) {
     float const v = x[i];
     float const l = level_f<Bounded>(mul(grid, sub(v, origin)));
     float const diff = sub(add(mul(step, l), base), v);
-    err = add(err, mul(add(average, fabsf(v)), mul(diff, diff)));
+    err = add(err, mul(w[i], mul(diff, diff)));
   }
   return err;
 }
 
 // The search over one group (make_qkx2_quants with n=32, nmax=15, rmin=-1, rdelta=0.1, nstep=20,
-// squared error; q4k.cpp:94-172).  x points at the group's 32 weights in shared memory.
-__device__ GroupFit fit_group(const float* x, float average) {
+// squared error; q4k.cpp:94-172).  x: the group's 32 weights, held in registers (every loop over them is
+// fully unrolled); the importance of a weight, average + |x|, is computed once.
+__device__ GroupFit fit_group(const float (&x)[32], float average) {
+  float w[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) w[i] = add(average, fabsf(x[i]));
   float lo = x[0], hi = x[0];
-  float sum_w = add(average, fabsf(x[0]));
+  float sum_w = w[0];
   float sum_x = mul(sum_w, x[0]);
-#pragma unroll 8
+#pragma unroll
   for (int i = 1; i < 32; ++i) {
-    float const v = x[i], w = add(average, fabsf(v));
+    float const v = x[i];
     if (v < lo) lo = v;
     if (v > hi) hi = v;
-    sum_w = add(sum_w, w);
-    sum_x = add(sum_x, mul(w, v));
+    sum_w = add(sum_w, w[i]);
+    sum_x = add(sum_x, mul(w[i], v));
   }
   float const x_min = lo;  // smallest weight, before the minimum is capped at zero
   if (lo > 0.f) lo = 0.f;
@@ -114,7 +118,7 @@ __device__ GroupFit fit_group(const float* x, float average) {
   }
   float grid = quo(15.f, sub(hi, lo));
   float scale = quo(1.f, grid);
-  float best = fit_error<false>(x, average, grid, lo, scale, lo);
+  float best = fit_error<false>(x, w, grid, lo, scale, lo);
   fit.grid = grid; fit.origin = lo;
   float floor_ = lo;  // the minimum candidates quantise against; moves when one is accepted
   for (int step = 0; step <= 20; ++step) {
@@ -123,7 +127,7 @@ __device__ GroupFit fit_group(const float* x, float average) {
     // Every grid * (x - origin) of this candidate is bounded by |grid| times the larger distance of
     // the extreme weights from the origin (rounding is monotonic); below 2^22 the float rounding applies.
     bool const bounded = mul(fabsf(cand_grid), fmaxf(fabsf(sub(hi, floor_)), fabsf(sub(x_min, floor_)))) < 4194304.f;
-    Moments const s = bounded ? moments<true>(x, average, cand_grid, floor_) : moments<false>(x, average, cand_grid, floor_);
+    Moments const s = bounded ? moments<true>(x, w, cand_grid, floor_) : moments<false>(x, w, cand_grid, floor_);
     float const det = sub(mul(sum_w, s.l2), mul(s.l, s.l));
     if (!(det > 0.f)) continue;
     float cand_scale = quo(sub(mul(sum_w, s.xl), mul(sum_x, s.l)), det);
@@ -132,8 +136,8 @@ __device__ GroupFit fit_group(const float* x, float average) {
       cand_min = 0.f;
       cand_scale = quo(s.xl, s.l2);
     }
-    float const err = bounded ? fit_error<true>(x, average, cand_grid, floor_, cand_scale, cand_min)
-                              : fit_error<false>(x, average, cand_grid, floor_, cand_scale, cand_min);
+    float const err = bounded ? fit_error<true>(x, w, cand_grid, floor_, cand_scale, cand_min)
+                              : fit_error<false>(x, w, cand_grid, floor_, cand_scale, cand_min);
     if (err < best) {
       best = err;
       scale = cand_scale;
@@ -178,11 +182,14 @@ __global__ void __launch_bounds__(kFitThreads) fit_q4k_kernel(const In* __restri
   uint64_t const b = block0 + (tid >> 3);
   uint32_t const g = tid & 7;
   bool const live = b < in_blocks;
-  const float* x = xs + tid * kRow;
+  float x[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) x[i] = xs[tid * kRow + i];
 
   // Admission of the inputs (q4k.cpp:189-200): the first offending weight of the block decides.
   uint8_t bad = kFitOk;
-  for (int i = 0; i < 32 && !bad; ++i) {
+#pragma unroll
+  for (int i = 31; i >= 0; --i) {
     float const v = x[i];
     if (!finite(v)) bad = kFitNonfinite;
     else if (fabsf(v) > 1.0e10f) bad = kFitRange;
@@ -198,6 +205,7 @@ __global__ void __launch_bounds__(kFitThreads) fit_q4k_kernel(const In* __restri
   bad = kFitOk;
   if (live && !block_flaw) {
     float lo = 0.f, hi = x[0], sum_x2 = 0.f;
+#pragma unroll
     for (int i = 0; i < 32; ++i) {
       float const v = x[i];
       if (v < lo) lo = v;
@@ -237,6 +245,7 @@ __global__ void __launch_bounds__(kFitThreads) fit_q4k_kernel(const In* __restri
   if (live && !block_flaw) {
     float const step = mul(__half2float(d16), float(sc6));
     float const offset = mul(__half2float(dmin16), float(mn6));
+#pragma unroll
     for (int i = 0; i < 32; ++i) {
       float const v = x[i];
       int const l = step != 0.f ? level(quo(add(v, offset), step)) : level(mul(fit.grid, sub(v, fit.origin)));
