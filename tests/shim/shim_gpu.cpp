@@ -1,4 +1,4 @@
-// Runs the quantiser, a projection and a decode entry through the C++23 shim on the current device.
+// Runs the quantiser, a projection, a decode entry and the fitter through the C++23 shim on the current device.
 // Weights are built so that every weight equals 1 (codes 1, six-bit scale 1, min 0, d = 1, dmin = 0) and the
 // activations are ones, so every output must equal k.
 #include <cuda_runtime.h>
@@ -45,6 +45,26 @@ int main() {
   CK(cudaMemcpy(&hf, fail, 4, cudaMemcpyDeviceToHost));
   int bad = hf != 0;
   for (size_t i = 0; i < h.size(); ++i) bad += std::fabs(h[i] - float(k)) > 1e-2f || h2[i] != h[i];
+  // Offline step through the shim: fit a weight whose rows repeat the ramp 0..15 (exactly representable
+  // levels), project ones through it: every output is close to the row sum, k / 16 * 120.
+  {
+    std::vector<float> wf(size_t(n) * k);
+    for (size_t i = 0; i < wf.size(); ++i) wf[i] = float(i % 16);
+    float* dw; std::uint8_t* st;
+    CK(cudaMalloc(&dw, wf.size() * 4)); CK(cudaMalloc(&st, size_t(n) * tiles_k));
+    CK(cudaMemcpy(dw, wf.data(), wf.size() * 4, cudaMemcpyHostToDevice));
+    if (auto r = quantize_q4k_weight(dw, false, w, {st, size_t(n) * tiles_k}, {fail, 1}, s); !r) { std::printf("fit: %s\n", r.error().detail.c_str()); return 1; }
+    if (auto r = q4k_q8_project(w, q, {out, size_t(m) * n}, s); !r) { std::printf("project fitted: %s\n", r.error().detail.c_str()); return 1; }
+    CK(cudaDeviceSynchronize());
+    std::vector<std::uint8_t> hs(size_t(n) * tiles_k);
+    CK(cudaMemcpy(hs.data(), st, hs.size(), cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(h.data(), out, h.size() * 4, cudaMemcpyDeviceToHost));
+    CK(cudaMemcpy(&hf, fail, 4, cudaMemcpyDeviceToHost));
+    bad += hf != 0;
+    for (auto v : hs) bad += v != static_cast<std::uint8_t>(FitStatus::Ok);
+    float const want = float(k) / 16.f * 120.f;
+    for (float v : h) bad += std::fabs(v - want) > 0.01f * want;
+  }
   std::printf(bad ? "shim gpu check failed (%d)\n" : "shim gpu check ok\n", bad);
   return bad != 0;
 }
