@@ -292,6 +292,12 @@ int q4k_validate_weight(const q4k_weight* weight, uint64_t* verdict, void* strea
  * reference GEMV sees. */
 int q4k_dequantize_bf16(const q4k_weight* weight, uint16_t* output, uint64_t output_len, void* stream);
 
+/* format::unpack_cuda_v0 (src/format/unpack.cpp:262-380) from the resident weight: levels int8 [n][k]
+ * (0..15, codes_len = n*k) and the 16 metadata bytes of every super-block [n][k/256][16]
+ * (metadata_len = n*(k/256)*16); k % 256 == 0.  The inverse of the pack inside q4k_fit_weight. */
+int q4k_unpack_logical(const q4k_weight* weight, int8_t* codes, uint64_t codes_len, uint8_t* metadata,
+                       uint64_t metadata_len, void* stream);
+
 /* Q4_K fitter on the device: compiler::quantize_q4k_block (src/compiler/quantization/q4k.cpp:186-278)
  * over every 256 consecutive weights, bit for bit (codes and the 16 metadata bytes).  The reference
  * runs it on the host, one block after another (quantize_fp32, src/compiler/quantization/quantizer.cpp:173-182).

@@ -85,6 +85,7 @@ SIGNATURES = {
     "q4k_repack_blocks144": (_i, [_vp, _u64, _u32, _u32, _vp, _u64, _vp, _u64, _vp]),
     "q4k_validate_weight": (_i, [_WP, _vp, _vp]),
     "q4k_dequantize_bf16": (_i, [_WP, _vp, _u64, _vp]),
+    "q4k_unpack_logical": (_i, [_WP, _vp, _u64, _vp, _u64, _vp]),
     "q4k_fit_blocks": (_i, [_vp, _u32, _u64, _vp, _vp, _vp, _vp, _vp]),
     "q4k_fit_weight": (_i, [_vp, _u32, _u32, _u32, _vp, _u64, _vp, _u64, _vp, _vp, _vp]),
     "q4k_q8_mlp_workspace_bytes": (_u64, [_u32, _u32, _u32]),

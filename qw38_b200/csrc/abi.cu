@@ -722,6 +722,23 @@ int q4k_dequantize_bf16(const q4k_weight* weight, uint16_t* output, uint64_t out
   return Q4K_OK;
 }
 
+int q4k_unpack_logical(const q4k_weight* weight, int8_t* codes, uint64_t codes_len, uint8_t* metadata, uint64_t metadata_len,
+                       void* stream) {
+  if (int st = valid_weight(weight, "q4k.unpack")) return st;
+  if (weight->k % 256 != 0 || codes_len != uint64_t(weight->n) * weight->k ||
+      metadata_len != uint64_t(weight->n) * (weight->k / 256) * 16)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q4k.unpack: invalid geometry");
+  Region regions[4] = {{weight->codes, weight->codes_bytes, 16, "codes"},
+                       {weight->scales, weight->scales_bytes, 16, "scales"},
+                       {codes, codes_len, 16, "logical codes"},
+                       {metadata, metadata_len, 16, "logical metadata"}};
+  if (int st = check_distinct(regions, 4, false)) return st;
+  Q4K_CUDA(q4k::launch_unpack_logical(static_cast<const uint8_t*>(weight->codes), static_cast<const uint8_t*>(weight->scales),
+                                      weight->n, weight->k, codes, metadata, static_cast<cudaStream_t>(stream)),
+           "q4k.unpack");
+  return Q4K_OK;
+}
+
 int q4k_fit_blocks(const void* weights, uint32_t weights_dtype, uint64_t blocks, int8_t* codes, uint8_t* metadata,
                    uint8_t* block_status, int* failure, void* stream) {
   if (!blocks || blocks > 0xffffffffull || weights_dtype > Q4K_FIT_BF16 || !failure)

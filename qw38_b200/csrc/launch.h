@@ -142,6 +142,9 @@ cudaError_t launch_fit_q4k(const void* weights, bool bf16, uint32_t rows, uint32
                            uint8_t* meta, uint8_t* status, int* failure, cudaStream_t stream);
 
 // repack.cu
+// int8 levels [n][k] and metadata [n][k/256][16] from split tiles (k % 256 == 0).
+cudaError_t launch_unpack_logical(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, int8_t* out_codes,
+                                  uint8_t* out_meta, cudaStream_t stream);
 // bf16 weights [n][k] (k % 256 == 0) from split tiles: bf16_rne((d*sc)*q - dmin*mn), each operation rounded.
 cudaError_t launch_dequantize_bf16(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, uint16_t* out,
                                    cudaStream_t stream);

@@ -113,6 +113,27 @@ __global__ void __launch_bounds__(256) dequantize_bf16_kernel(const uint8_t* __r
   }
 }
 
+// Split tiles -> the logical form of format::unpack_cuda_v0 (src/format/unpack.cpp:262-380): int8 levels
+// [n][k] and the 16 metadata bytes per super-block [n][k/256][16].  Same block shape as the dequantiser.
+__global__ void __launch_bounds__(256) unpack_logical_kernel(const uint8_t* __restrict__ codes, const uint8_t* __restrict__ meta,
+                                                             uint32_t n, uint32_t tiles_k, uint32_t chunks_k,
+                                                             int8_t* __restrict__ out_codes, uint8_t* __restrict__ out_meta) {
+  uint32_t const group = blockIdx.x / chunks_k, kb0 = (blockIdx.x % chunks_k) * kDeqTiles;
+  uint32_t const r = threadIdx.x >> 5, c = threadIdx.x & 31;
+  uint32_t const row = group * 8 + r;
+  if (row >= n) return;
+  auto spread = [](uint32_t n4) { return (n4 & 15u) | ((n4 & 0xf0u) << 4) | ((n4 & 0xf00u) << 8) | ((n4 & 0xf000u) << 12); };
+#pragma unroll
+  for (int t = 0; t < kDeqTiles; ++t) {
+    if (kb0 + t >= tiles_k) break;
+    uint64_t const tr = (uint64_t(group) * tiles_k + kb0 + t) * 8 + r;
+    uint32_t const w = __ldg(reinterpret_cast<const uint32_t*>(codes) + tr * 32 + c);
+    uint64_t const block = uint64_t(row) * tiles_k + kb0 + t;
+    *reinterpret_cast<uint2*>(out_codes + block * 256 + 8 * c) = make_uint2(spread(w & 0xffffu), spread(w >> 16));
+    if (c < 4) reinterpret_cast<uint32_t*>(out_meta + block * 16)[c] = __ldg(reinterpret_cast<const uint32_t*>(meta + tr * 16) + c);
+  }
+}
+
 // verdict[1] holds the winning key on entry; rewrites verdict as {kind, byte offset in its span}.
 __global__ void validate_verdict_kernel(unsigned long long* verdict) {
   unsigned long long const key = verdict[1];
@@ -146,6 +167,15 @@ cudaError_t launch_dequantize_bf16(const uint8_t* codes, const uint8_t* meta, ui
   uint64_t const blocks = uint64_t((n + 7) / 8) * chunks_k;
   if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
   dequantize_bf16_kernel<<<unsigned(blocks), 256, 0, stream>>>(codes, meta, n, tiles_k, chunks_k, out);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_unpack_logical(const uint8_t* codes, const uint8_t* meta, uint32_t n, uint32_t k, int8_t* out_codes,
+                                  uint8_t* out_meta, cudaStream_t stream) {
+  uint32_t const tiles_k = k / 256, chunks_k = (tiles_k + kDeqTiles - 1) / kDeqTiles;
+  uint64_t const blocks = uint64_t((n + 7) / 8) * chunks_k;
+  if (blocks > 0x7fffffffull) return cudaErrorInvalidValue;
+  unpack_logical_kernel<<<unsigned(blocks), 256, 0, stream>>>(codes, meta, n, tiles_k, chunks_k, out_codes, out_meta);
   return cudaGetLastError();
 }
 

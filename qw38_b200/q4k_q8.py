@@ -365,6 +365,17 @@ def dequantize_bf16(weight: PrefillWeight, stream=None) -> torch.Tensor:
     return out
 
 
+def unpack_logical(weight: PrefillWeight, stream=None):
+    """format::unpack_cuda_v0 (src/format/unpack.cpp:262-380) from the resident weight:
+    (levels int8 [n, k], metadata uint8 [n, k/256, 16])."""
+    dev = weight.codes.device
+    codes = torch.empty((weight.n, weight.k), dtype=torch.int8, device=dev)
+    meta = torch.empty((weight.n, weight.k // 256, 16), dtype=torch.uint8, device=dev)
+    _check(L.load().q4k_unpack_logical(C.byref(weight.c_struct()), _ptr(codes), codes.numel(), _ptr(meta), meta.numel(),
+                                       _stream(stream)))
+    return codes, meta
+
+
 FIT_ERRORS = {
     1: "Q4_K input is nonfinite",
     2: "Q4_K fitting range exceeded",

@@ -148,3 +148,23 @@ def test_dequantise_rejects_wrong_output_length():
     out = torch.zeros(16 * 256 + 8, dtype=torch.bfloat16, device="cuda")
     st = L.load().q4k_dequantize_bf16(ctypes.byref(w.c_struct()), ctypes.c_void_p(out.data_ptr()), out.numel(), None)
     assert st == L.ERR_INVALID_ARGUMENT and not out.any()
+
+
+# ---- q4k_unpack_logical: format::unpack_cuda_v0 from the resident weight ------------------------------
+
+def test_unpack_matches_reference_vectors(golden):
+    from qw38_b200.q4k_q8 import unpack_logical
+    w = PrefillWeight.from_host(golden["a_packed_codes"], golden["a_packed_scales"], 137, 512)
+    codes, meta = unpack_logical(w)
+    assert np.array_equal(codes.cpu().numpy(), golden["a_codes"])
+    assert np.array_equal(meta.cpu().numpy(), golden["a_meta"])
+
+
+@pytest.mark.parametrize("n,k", [(21, 768), (1021, 5120), (64, 17408)])
+def test_fit_pack_unpack_round_trip(n, k):
+    from qw38_b200.q4k_q8 import quantize_q4k_blocks, unpack_logical
+    torch.manual_seed(n)
+    w = torch.randn(n, k, device="cuda") * 0.03
+    codes, meta, status = quantize_q4k_blocks(w)
+    ucodes, umeta = unpack_logical(quantize_q4k_weight(w))
+    assert torch.equal(ucodes.reshape(-1, 256), codes) and torch.equal(umeta.reshape(-1, 16), meta)
