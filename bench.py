@@ -532,6 +532,20 @@ def main():
             prefill[f"M{m}_N{n}_K{k}"] = {"ms": round(t, 4), "int8_TOPS": round(tops, 1), "kernel": "mmq_tcgen05_kernel",
                                           "frac_of_2x_measured_bf16": round(tops / int8_peak, 4),
                                           "frac_of_nominal_4500": round(tops / 4500.0, 4)}
+            # comparator: the reference's other prefill route on this GPU, unpack to bf16 (timed under "fitter") + library GEMM
+            from qw38_b200.q4k_q8 import dequantize_bf16
+            wb = dequantize_bf16(w)
+            xb = (torch.randn((m, k), device=dev, generator=g) * 0.5).to(torch.bfloat16)
+            with torch.cuda.stream(stream):
+                for _ in range(3):
+                    torch.matmul(xb, wb.t())
+                e0.record(stream)
+                for _ in range(reps):
+                    torch.matmul(xb, wb.t())
+                e1.record(stream)
+            stream.synchronize()
+            prefill[f"M{m}_N{n}_K{k}"]["bf16_library_gemm_ms"] = round(e0.elapsed_time(e1) / reps, 4)
+            del wb, xb
             del w, out, xq
         # config[3]: packed ragged batch, 48 single-row requests + 512 + 237 + 1024 rows = 1821 rows
         from qw38_b200.q4k_q8 import q4k_q8_project_ragged

@@ -365,6 +365,19 @@ def dequantize_bf16(weight: PrefillWeight, stream=None) -> torch.Tensor:
     return out
 
 
+def prefill_project_bf16(weight: PrefillWeight, x: torch.Tensor, weight_bf16: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The reference's OTHER prefill route (PrefillDispatch's BF16 path, cuda/prefill.cu:329-335,510-560):
+    unpack the Q4_K weight to bf16 and multiply by the bf16 activations in a library GEMM with fp32
+    accumulation.  x: bfloat16 [m, k]; returns bfloat16 [m, n].  The weights are bit-identical to
+    dequantize_to_bf16; the result is NOT the Q8 equation (activations are not quantised), so it is held
+    to the tolerance of the reference's BF16 path, not to the integer contract.  Pass weight_bf16 (from
+    dequantize_bf16) to reuse the unpacked weight across calls."""
+    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != weight.k:
+        raise Q4KError(L.ERR_INVALID_ARGUMENT, "prefill_project_bf16 takes bfloat16 [m, k] activations")
+    wb = dequantize_bf16(weight) if weight_bf16 is None else weight_bf16
+    return torch.matmul(x, wb.t())
+
+
 def unpack_logical(weight: PrefillWeight, stream=None):
     """format::unpack_cuda_v0 (src/format/unpack.cpp:262-380) from the resident weight:
     (levels int8 [n, k], metadata uint8 [n, k/256, 16])."""
