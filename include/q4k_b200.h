@@ -188,11 +188,37 @@ void q4k_set_launch_overlap(int enabled);
 int q4k_get_launch_overlap(void);
 
 /* Synchronises the current device and reads the status word shared by the kernels that wait on
- * device-side barriers (tcgen05, TMA gemv, peer wait; library-owned scratch): 0 = every launch so
- * far ran to completion; nonzero = a bounded wait gave up at that site (0x5xx TMA gemv, 0x610 peer
- * wait, others tcgen05) and the affected block returned without writing its outputs.  A nonzero
- * word is cleared by the read.  No counterpart in the reference, whose kernels have no device-side waits. */
+ * device-side barriers (tcgen05, TMA gemv, peer wait): 0 = every launch so far ran to completion;
+ * nonzero = a bounded wait gave up at that site (0x5xx TMA gemv, 0x610 peer wait, 0x71x the int8
+ * peak measurement, others tcgen05) and the affected block returned without writing its outputs.
+ * The word is a static device variable of the library (one per device, no allocation), whatever
+ * scratch the launches used.  A nonzero word is cleared by the read, and the arrival counters of the
+ * library-owned split-K scratch are zeroed with it (a launch that gave up may have left some behind;
+ * a caller that passes its own workspace has them cleared on every call anyway).
+ * No counterpart in the reference, whose kernels have no device-side waits. */
 int q4k_kernel_status(int* value);
+
+/* Split-K scratch owned by the library (no counterpart in the reference, whose kernels have no split-K).
+ * q4k_q8_project, _ex without a workspace, _ragged, _gather and the decode / prefill / MLP entries keep
+ * their split-K partial tiles and arrival counters in ONE buffer per device, allocated on first need
+ * (8 MiB) and replaced by a larger one when a call needs more.  What that means for the caller:
+ *  - It is per device, not per stream.  Two streams that run split-K projections at the same time race
+ *    on it; give such calls their own q4k_project_options.workspace, or serialise them.
+ *  - A block that was handed out is never freed or moved (launches in flight and captured graphs keep
+ *    its address); a replaced block stays allocated until the process ends.
+ *  - A call that would have to grow the buffer while its stream is capturing is rejected with
+ *    Q4K_ERR_INVALID_ARGUMENT.  q4k_reserve_scratch(bytes, stream) grows it ahead of time: call it once
+ *    per device, before capturing, with the largest split_k * m * n * 4 the captured calls will need
+ *    (q4k_project_workspace_bytes gives the figure for one call). */
+int q4k_reserve_scratch(uint64_t partial_bytes, void* stream);
+
+/* Dense int8 tensor throughput of the current device, measured with the prefill kernel's own
+ * instruction (tcgen05.mma kind::i8, M128 x N256 x K32, operands resident in shared memory): every SM
+ * issues mmas_per_sm MMAs back to back; *tops = 2*128*256*32 * MMAs / time, time by CUDA events around
+ * the launch (returned in *milliseconds when given).  Synchronises the stream.  The reference records
+ * its tensor peak as unknown (docs/architecture/cuda-hardware-model.md:57,299); this is the
+ * denominator of the prefill roofline. */
+int q4k_measure_int8_peak(uint32_t mmas_per_sm, double* tops, double* milliseconds, void* stream);
 
 /* Padding rules (decode_pad_n / decode_pad_k / decode_code_bytes / decode_scale_bytes,
  * cuda/decode_mmv.hpp:148-205, Q4_K branch). */
@@ -223,7 +249,8 @@ int q4k_export_q8_1(q4k_q8_input input, uint8_t* records, uint64_t records_bytes
 /* q4k_q8_project (cuda/q4k_q8.hpp:35-37, cuda/q4k_q8.cu:332-345):
  * out[token*n + row] = sum_g a[token,g]*((d*sc_g)*dot_g - (dmin*m_g)*sum[token,g]) (+ residual).
  * residual may be NULL (residual_len 0).  The first call on a device may allocate the
- * library-owned split-K scratch; make one call per device before capturing a graph. */
+ * library-owned split-K scratch (see q4k_reserve_scratch): it is shared by all streams of the device,
+ * and must be large enough before a graph is captured. */
 int q4k_q8_project(const q4k_weight* weight, q4k_q8_input input, float* output,
                    uint64_t output_len, const float* residual, uint64_t residual_len,
                    void* stream);

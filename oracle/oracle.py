@@ -35,9 +35,12 @@ def build(native: bool = False) -> Path:
     return out
 
 
-def build_ref(reference_root: str = "/root/reference") -> Path | None:
-    """Compile the reference's host sources where they lie (see oracle/Makefile)."""
-    if not (Path(reference_root) / "src" / "format").is_dir():
+def build_ref(reference_root: str | None = None) -> Path | None:
+    """Compile the reference's host sources where they lie (see oracle/Makefile).  The checkout is named by
+    the argument, by the environment variable QW38_REFERENCE_ROOT, or is a directory "reference" beside this
+    repository; when none of them holds the sources nothing is built and an existing library is used as it is."""
+    reference_root = reference_root or os.environ.get("QW38_REFERENCE_ROOT") or str(HERE.parent.parent / "reference")
+    if not reference_root or not (Path(reference_root) / "src" / "format").is_dir():
         return REF_SO if REF_SO.exists() else None
     subprocess.run(["make", "-C", str(HERE), "ref", f"REF={reference_root}"], check=True,
                    stdout=subprocess.DEVNULL)
@@ -81,6 +84,26 @@ def ref() -> C.CDLL | None:
 
 def num_threads() -> int:
     return lib().orc_num_threads()
+
+
+def set_threads(threads: int, handle=None) -> int:
+    """OpenMP team size of `handle` (a library returned by lib(); each loaded copy has its own OpenMP state)."""
+    return (handle if handle is not None else lib()).orc_set_threads(int(threads))
+
+
+def ref_gemv_packed(wcodes: np.ndarray, wmeta: np.ndarray, n: int, k: int, x_bits: np.ndarray) -> np.ndarray | None:
+    """compiler::reference_gemv_packed (src/compiler/quantization/reference.cpp:230-279) from the reference's own
+    host code: split-tile weight x bf16 activations (bit patterns) -> fp32 [n].  None when that library was not built."""
+    r = ref()
+    if r is None:
+        return None
+    y = np.zeros(n, dtype=np.float32)
+    wc, wm = np.ascontiguousarray(wcodes), np.ascontiguousarray(wmeta)
+    st = r.ref_gemv_packed_q4k(C.c_uint64(n), C.c_uint64(k), _p(wc), C.c_uint64(wc.size), _p(wm), C.c_uint64(wm.size),
+                               _p(np.ascontiguousarray(x_bits, dtype=np.uint16)), _p(y))
+    if st != 0:
+        raise RuntimeError("reference_gemv_packed refused the operands")
+    return y
 
 
 # ---------------------------------------------------------------------------

@@ -438,3 +438,16 @@ int orc_num_threads(void) {
   return 1;
 #endif
 }
+
+/* Sets the OpenMP team size for the calls that follow (a launcher may export OMP_NUM_THREADS=1 to every
+ * rank; the timed CPU baseline wants all host cores whatever the environment says).  Returns the size in
+ * effect afterwards. */
+int orc_set_threads(int threads) {
+#ifdef _OPENMP
+  if (threads > 0) omp_set_num_threads(threads);
+  return omp_get_max_threads();
+#else
+  (void)threads;
+  return 1;
+#endif
+}

@@ -58,6 +58,8 @@ SIGNATURES = {
     "q4k_last_cuda_status": (_i, []),
     "q4k_abi_version": (_u32, []),
     "q4k_kernel_status": (_i, [C.POINTER(_i)]),
+    "q4k_reserve_scratch": (_i, [_u64, _vp]),
+    "q4k_measure_int8_peak": (_i, [_u32, C.POINTER(C.c_double), C.POINTER(C.c_double), _vp]),
     "q4k_set_launch_overlap": (None, [_i]),
     "q4k_get_launch_overlap": (_i, []),
     "q4k_pad_n": (_u64, [_u32]),

@@ -9,7 +9,7 @@ from pathlib import Path
 PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 LIB = PKG / "lib" / "libq4k_b200.so"
-SOURCES = ["abi.cu", "q8_quantize.cu", "gemv_dp4a.cu", "gemv_mma.cu", "gemv_tma.cu", "mmq_mma.cu", "mmq_tcgen05.cu", "repack.cu", "no_alloc.cu", "peer.cu", "decode_entry.cu", "gemv_bf16w.cu", "fit_q4k.cu"]
+SOURCES = ["abi.cu", "q8_quantize.cu", "gemv_dp4a.cu", "gemv_mma.cu", "gemv_tma.cu", "mmq_mma.cu", "mmq_tcgen05.cu", "repack.cu", "no_alloc.cu", "peer.cu", "decode_entry.cu", "gemv_bf16w.cu", "fit_q4k.cu", "int8_peak.cu"]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
     "-Xcompiler", "-fPIC",

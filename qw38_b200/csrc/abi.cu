@@ -14,6 +14,7 @@
 #include <limits>
 #include <atomic>
 #include <mutex>
+#include <vector>
 
 #include "../../include/q4k_b200.h"
 #include "launch.h"
@@ -129,8 +130,16 @@ q4k::WeightView view(const q4k_weight& w) {
 q4k::Q8View view(const q4k_q8_input& x) { return {x.codes, x.scales, x.sums, x.m, x.padded_k}; }
 q4k::Q8Out out_view(const q4k_q8_input& x) { return {x.codes, x.scales, x.sums, x.m, x.padded_k}; }
 
-// Library-owned split-K scratch, one per device: [ticket region | fp32 partial tiles].
-// Tickets are zeroed at allocation and every kernel leaves them zero.
+// Status word of the kernels that wait on device-side barriers: one per device, in the library's own
+// device image, so that it exists without any allocation and whatever scratch a call uses.
+__device__ int g_kernel_status_word;
+std::mutex g_status_mutex;
+int* g_status_address[64];
+
+// Library-owned split-K scratch, one chain per device: [ticket region | fp32 partial tiles].
+// Tickets are zeroed at allocation and every kernel leaves them zero.  A block is never freed or
+// moved once handed out: launches in flight and captured graphs keep its address, so growing
+// allocates a larger block and retires the old one (kept until the process ends).
 constexpr uint64_t kTicketRegion = 256 * 1024;
 struct Scratch {
   void* p = nullptr;
@@ -138,8 +147,9 @@ struct Scratch {
 };
 std::mutex g_scratch_mutex;
 Scratch g_scratch[64];
+std::vector<Scratch> g_retired[64];
 
-int own_scratch(uint64_t partial_bytes, void** out) {
+int own_scratch(uint64_t partial_bytes, void** out, cudaStream_t stream) {
   int device = 0;
   Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
   if (device < 0 || device >= 64) return fail(Q4K_ERR_INVALID_ARGUMENT, "device ordinal out of range");
@@ -147,16 +157,39 @@ int own_scratch(uint64_t partial_bytes, void** out) {
   Scratch& s = g_scratch[device];
   uint64_t const need = kTicketRegion + partial_bytes;
   if (s.bytes < need) {
-    // Growing synchronises the device: earlier launches may still use the old block.
-    Q4K_CUDA(cudaDeviceSynchronize(), "scratch.sync");
-    if (s.p) Q4K_CUDA(cudaFree(s.p), "scratch.free");
-    s = Scratch{};
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess) (void)cudaGetLastError();
+    if (cap != cudaStreamCaptureStatusNone)
+      return fail(Q4K_ERR_INVALID_ARGUMENT,
+                  "split-K scratch of %llu bytes is needed while the stream is capturing: call q4k_reserve_scratch first",
+                  static_cast<unsigned long long>(partial_bytes));
     uint64_t const bytes = need < (8ull << 20) ? (8ull << 20) : (need + (1ull << 20) - 1) / (1ull << 20) * (1ull << 20);
-    Q4K_CUDA(cudaMalloc(&s.p, bytes), "scratch.alloc");
-    Q4K_CUDA(cudaMemset(s.p, 0, kTicketRegion), "scratch.clear");
+    void* p = nullptr;
+    Q4K_CUDA(cudaMalloc(&p, bytes), "scratch.alloc");
+    cudaError_t st = cudaMemset(p, 0, kTicketRegion);
+    if (st != cudaSuccess) { (void)cudaFree(p); return fail_cuda(st, "scratch.clear"); }
+    if (s.p) g_retired[device].push_back(s);
+    s.p = p;
     s.bytes = bytes;
   }
   *out = s.p;
+  return Q4K_OK;
+}
+
+// Caller-provided scratch: checked like every other operand, tickets cleared on the stream.
+int caller_scratch(const q4k_project_options* opt, uint64_t partial_bytes, uint64_t ticket_bytes, bool trusted,
+                   cudaStream_t stream, void** out) {
+  if (opt->workspace_bytes < kTicketRegion + partial_bytes || ticket_bytes > kTicketRegion)
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: workspace too small");
+  if (!trusted) {
+    int device = 0;
+    Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+    if (int st = check_span(Region{opt->workspace, opt->workspace_bytes, 256, "workspace"}, device)) return st;
+  } else if (reinterpret_cast<uintptr_t>(opt->workspace) % 256 != 0) {
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "workspace: misaligned pointer");
+  }
+  if (ticket_bytes) Q4K_CUDA(cudaMemsetAsync(opt->workspace, 0, ticket_bytes, stream), "q4k_q8.clear_tickets");
+  *out = opt->workspace;
   return Q4K_OK;
 }
 
@@ -223,14 +256,12 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
     uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
     void* scratch = nullptr;
     if (opt && opt->workspace) {
-      if (opt->workspace_bytes < kTicketRegion + partial_bytes)
-        return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: workspace too small");
-      scratch = opt->workspace;
-      Q4K_CUDA(cudaMemsetAsync(scratch, 0, kTicketRegion, stream), "q4k_q8.clear_tickets");
-    } else if (int st = own_scratch(partial_bytes, &scratch)) {
+      if (int st = caller_scratch(opt, partial_bytes, plan.split_k > 1 ? uint64_t(plan.ranges) * 4 : 0, trusted, stream, &scratch)) return st;
+    } else if (int st = own_scratch(partial_bytes, &scratch, stream)) {
       return st;
     }
-    int* status = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch) + kTicketRegion - 4);
+    int* status = q4k::kernel_status_word();
+    if (!status) return Q4K_ERR_STATUS;
     Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), output, res, partials, plan,
                                   static_cast<uint8_t*>(scratch) + kTicketRegion, static_cast<uint32_t*>(scratch),
                                   status, stream),
@@ -247,15 +278,13 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
     uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
     void* scratch = nullptr;
     if (opt && opt->workspace) {
-      if (opt->workspace_bytes < kTicketRegion + partial_bytes)
-        return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: workspace too small");
-      scratch = opt->workspace;
-      Q4K_CUDA(cudaMemsetAsync(scratch, 0, kTicketRegion, stream), "q4k_q8.clear_tickets");
-    } else if (int st = own_scratch(partial_bytes, &scratch)) {
+      if (int st = caller_scratch(opt, partial_bytes, plan.split_k > 1 ? tiles * 4 : 0, trusted, stream, &scratch)) return st;
+    } else if (int st = own_scratch(partial_bytes, &scratch, stream)) {
       return st;
     }
-    int* status = reinterpret_cast<int*>(static_cast<uint8_t*>(scratch) + kTicketRegion - 4);
-    Q4K_CUDA(q4k::launch_mmq_tcgen05(view(w), view(x), output, res, partials, plan,
+    int* status = q4k::kernel_status_word();
+    if (!status) return Q4K_ERR_STATUS;
+    Q4K_CUDA(q4k::launch_mmq_tcgen05(view(w), view(x), q4k::tc_output(output, res), partials, plan,
                                      static_cast<uint8_t*>(scratch) + kTicketRegion, static_cast<uint32_t*>(scratch),
                                      status, stream),
              "q4k_q8.mmq_tcgen05");
@@ -270,17 +299,8 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
         return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: too many tiles for split-K");
       uint64_t const partial_bytes = uint64_t(plan.split_k) * x.m * w.n * 4;
       if (opt && opt->workspace) {
-        if (opt->workspace_bytes < kTicketRegion + partial_bytes)
-          return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: workspace too small");
-        if (!trusted) {
-          Region ws{opt->workspace, opt->workspace_bytes, 256, "workspace"};
-          int device = 0;
-          Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
-          if (int st = check_span(ws, device)) return st;
-        }
-        scratch = opt->workspace;
-        Q4K_CUDA(cudaMemsetAsync(scratch, 0, row_tiles * token_tiles * 4, stream), "q4k_q8.clear_tickets");
-      } else if (int st = own_scratch(partial_bytes, &scratch)) {
+        if (int st = caller_scratch(opt, partial_bytes, row_tiles * token_tiles * 4, trusted, stream, &scratch)) return st;
+      } else if (int st = own_scratch(partial_bytes, &scratch, stream)) {
         return st;
       }
     }
@@ -322,6 +342,28 @@ int set_error(int code, const char* fmt, ...) {
   return code;
 }
 int set_error_cuda(cudaError_t status, const char* operation) { return fail_cuda(status, operation); }
+int* kernel_status_word() {
+  int device = 0;
+  if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+    (void)cudaGetLastError();
+    fail(Q4K_ERR_STATUS, "kernel status word: no current device");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_status_mutex);
+  if (!g_status_address[device]) {
+    void* p = nullptr;
+    cudaError_t st = cudaGetSymbolAddress(&p, g_kernel_status_word);
+    if (st != cudaSuccess) { fail_cuda(st, "kernel status word"); return nullptr; }
+    g_status_address[device] = static_cast<int*>(p);
+  }
+  return g_status_address[device];
+}
+int check_operands(const Operand* operands, int count) {
+  Region regions[16];
+  if (count > 16) return fail(Q4K_ERR_INVALID_ARGUMENT, "too many operands");
+  for (int i = 0; i < count; ++i) regions[i] = Region{operands[i].p, operands[i].bytes, operands[i].alignment, operands[i].name};
+  return check_distinct(regions, count, false);
+}
 }  // namespace q4k
 
 extern "C" {
@@ -341,18 +383,27 @@ uint64_t q4k_scale_bytes(uint32_t padded_n, uint32_t padded_k) { return uint64_t
 int q4k_kernel_status(int* value) {
   if (!value) return fail(Q4K_ERR_INVALID_ARGUMENT, "kernel_status: null output");
   *value = 0;
-  int device = 0;
-  Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
-  void* p = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(g_scratch_mutex);
-    if (device >= 0 && device < 64) p = g_scratch[device].p;
-  }
-  if (!p) return Q4K_OK;  // nothing has used the library-owned scratch yet
+  int* word = q4k::kernel_status_word();
+  if (!word) return Q4K_ERR_STATUS;
   Q4K_CUDA(cudaDeviceSynchronize(), "kernel_status.sync");
-  Q4K_CUDA(cudaMemcpy(value, static_cast<uint8_t*>(p) + kTicketRegion - 4, 4, cudaMemcpyDeviceToHost), "kernel_status.read");
-  if (*value != 0) Q4K_CUDA(cudaMemset(static_cast<uint8_t*>(p) + kTicketRegion - 4, 0, 4), "kernel_status.clear");
+  Q4K_CUDA(cudaMemcpy(value, word, 4, cudaMemcpyDeviceToHost), "kernel_status.read");
+  if (*value != 0) {
+    // A launch that gave up may have left split-K tickets of the library's scratch behind: start clean.
+    Q4K_CUDA(cudaMemset(word, 0, 4), "kernel_status.clear");
+    int device = 0;
+    Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (device >= 0 && device < 64) {
+      if (g_scratch[device].p) Q4K_CUDA(cudaMemset(g_scratch[device].p, 0, kTicketRegion), "kernel_status.tickets");
+      for (auto const& r : g_retired[device]) Q4K_CUDA(cudaMemset(r.p, 0, kTicketRegion), "kernel_status.tickets");
+    }
+  }
   return Q4K_OK;
+}
+
+int q4k_reserve_scratch(uint64_t partial_bytes, void* stream) {
+  void* p = nullptr;
+  return own_scratch(partial_bytes, &p, static_cast<cudaStream_t>(stream));
 }
 
 int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gather_desc* desc, const float* residual,
@@ -383,8 +434,10 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
   q4k::GemvTmaPlan plan = q4k::plan_gemv_tma(x.m, w.n, w.padded_k / 256, 0, 0);
   uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
   void* scratch = nullptr;
-  if (int st = own_scratch(partial_bytes, &scratch)) return st;
+  if (int st = own_scratch(partial_bytes, &scratch, stream)) return st;
   uint8_t* const base = static_cast<uint8_t*>(scratch);
+  int* const status = q4k::kernel_status_word();
+  if (!status) return Q4K_ERR_STATUS;
   q4k::GemvTmaGather gather{};
   for (uint32_t g = 0; g < desc->ranks; ++g) { gather.outputs[g] = desc->outputs[g]; gather.flags[g] = desc->flags[g]; }
   // words 8 and 9 of this rank's own flag array: its unannounced projections and the block counter
@@ -393,7 +446,7 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
   gather.ranks = desc->ranks; gather.rank = desc->rank; gather.row_offset = desc->row_offset; gather.total_rows = desc->total_rows;
   Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), nullptr, residual_len ? residual : nullptr, nullptr, plan,
                                 base + kTicketRegion, reinterpret_cast<uint32_t*>(base),
-                                reinterpret_cast<int*>(base + kTicketRegion - 4), stream, &gather),
+                                status, stream, &gather),
            "q4k_q8.gemv_tma_gather");
   return Q4K_OK;
 }
@@ -404,11 +457,10 @@ static int peer_wait_impl(const q4k_gather_desc* desc, long long limit, void* st
   for (uint32_t g = 0; g < desc->ranks; ++g)
     if (!desc->flags[g] || reinterpret_cast<uintptr_t>(desc->flags[g]) % 4 != 0)
       return fail(Q4K_ERR_INVALID_ARGUMENT, "peer_wait: every rank needs a 4-byte aligned flag array");
-  void* scratch = nullptr;
-  if (int st = own_scratch(0, &scratch)) return st;
-  uint8_t* const base = static_cast<uint8_t*>(scratch);
-  Q4K_CUDA(q4k::launch_peer_wait(desc->flags, desc->flags[desc->rank] + 8, desc->ranks, desc->rank, limit,
-                                 reinterpret_cast<int*>(base + kTicketRegion - 4), static_cast<cudaStream_t>(stream_handle)),
+  int* const status = q4k::kernel_status_word();
+  if (!status) return Q4K_ERR_STATUS;
+  Q4K_CUDA(q4k::launch_peer_wait(desc->flags, desc->flags[desc->rank] + 8, desc->ranks, desc->rank, limit, status,
+                                 static_cast<cudaStream_t>(stream_handle)),
            "peer_wait");
   return Q4K_OK;
 }

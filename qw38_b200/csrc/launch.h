@@ -60,11 +60,31 @@ struct TcPlan {
   uint32_t ntok;
   uint32_t split_k;
 };
+// Where the rows go: element (token, row) lands at token * stride + row0 + row of every fp32 destination
+// (one buffer, or each rank's copy of a gathered output, written with plain peer stores), or of the one
+// bf16 destination (round to nearest even).  residual, if set, has the destination's geometry and is
+// added last.  stride 0 = the weight's own n.
+// Row-sharded use (flags / done / unsignalled as in GemvTmaGather below): done != nullptr makes the launch count
+// itself as a finished projection of `rank`.
+struct TcOutput {
+  float* out[8];
+  uint16_t* out_bf16;
+  const float* residual;
+  uint32_t ndst, stride, row0;
+  uint32_t* flags[8];
+  uint32_t* done;
+  uint32_t* unsignalled;
+  uint32_t rank;
+};
+inline TcOutput tc_output(float* out, const float* residual) {
+  TcOutput o{};
+  o.out[0] = out; o.residual = residual; o.ndst = 1;
+  return o;
+}
 bool tcgen05_supported(const WeightView& w, const Q8View& x);
 TcPlan plan_tcgen05(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request);
-cudaError_t launch_mmq_tcgen05(const WeightView& w, const Q8View& x, float* out, const float* residual,
-                               int32_t* partials, const TcPlan& plan, void* partial_tiles, uint32_t* tickets,
-                               int* status, cudaStream_t stream);
+cudaError_t launch_mmq_tcgen05(const WeightView& w, const Q8View& x, const TcOutput& out, int32_t* partials,
+                               const TcPlan& plan, void* partial_tiles, uint32_t* tickets, int* status, cudaStream_t stream);
 
 // gemv_tma.cu : m <= 16.  Weights streamed by TMA into a shared-memory ring, activations held in
 // registers by warps that each own one super-block column of the block's K slice; K slices of
@@ -135,6 +155,18 @@ cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
 // abi.cu : records the thread-local error text behind q4k_last_error() and returns `code`.
 int set_error(int code, const char* fmt, ...);
 int set_error_cuda(cudaError_t status, const char* operation);
+// abi.cu : device address of the current device's kernel status word (a __device__ int of the library, resolved once
+// per device with cudaGetSymbolAddress; nothing is allocated).  nullptr + thread-local error text on failure.
+int* kernel_status_word();
+// abi.cu : the host-side operand checks of the projection entries for entry points in other files: every span non-empty,
+// aligned, device memory of the current device inside one allocation, and pairwise disjoint.
+struct Operand {
+  const void* p;
+  uint64_t bytes;
+  uint32_t alignment;
+  const char* name;
+};
+int check_operands(const Operand* operands, int count);
 
 // fit_q4k.cu: weights [rows][tiles_k*256] (fp32, or bf16 bits) -> Q4_K.  split = false writes int8 codes
 // [blocks][256] + metadata [blocks][16]; split = true writes the split-tile layout for ceil8(rows) rows.

@@ -2,25 +2,45 @@
 // by TMA, one TMEM accumulator per K32 group, scaling epilogue on CUDA cores.
 //
 // The per-K32 rule of the reference (cuda/q4k_q8.cu:70-72: one exact int32 dot per 32 columns,
-// never carried into the next group) fixes the structure: every MMA has K = 32, starts from a
-// cleared accumulator, and its 128 x NTOK int32 results are drained from TMEM and folded into
-// fp32 accumulators in registers as  acc += a * (D * float(P) - Mn * float(sum)).
+// never carried into the next group) fixes the structure: every data MMA has K = 32 and its
+// 128 x NTOK int32 results are drained from TMEM and folded into fp32 accumulators in registers
+// as  acc += a * (D * float(P)) - Mn * (a * float(sum)).
+//
+// Two resources bound such a kernel, and the design is built around both:
+//   * The fp32 pipe: three FMAs per partial is the floor of the equation, so nothing else may
+//     run there.  No int -> float conversion: before the data MMA of a group a second MMA of two
+//     constant tiles (every byte 64) writes 32 * 64 * 64 = 2^17 into every accumulator, and the
+//     data MMA accumulates on top.  The int32 word 2^17 + P, read as an fp32 bit pattern, is the
+//     (sub)normal number (2^17 + P) * 2^-149, an affine function of P, so one FMA with the row's
+//     scale S = D * 2^100 and the exact constant c = -D * 2^-32 yields D * P * 2^-49 with a single
+//     rounding.  The activation scale carries the inverse power of two, a' = a * 2^49, so the
+//     second FMA acc += a' * v is the reference's a * (D * P) to the bit.  Should a' overflow
+//     (|x| beyond ~5e27) the super-block takes a slower loop that reads the plain scale.
+//   * The shared-memory pipe: one wavefront per clock per SM.  An epilogue in which a thread owns
+//     one weight row and 32 tokens reads 32 activation scales per group as broadcasts, 4 bytes
+//     per wavefront, and saturates that pipe at a fifth of the fp32 floor.  So the accumulators
+//     are read in the 16x256b shape (the MMA C-fragment layout): a thread owns 4 rows x 8
+//     tokens of its warp's 32 x 32 patch, needs the scales of 8 tokens and 4 rows only, and a
+//     warp's loads are 64-byte segments instead of broadcasts.  The row scales come from a table
+//     the expander warps build once per super-block; the expanders themselves read and write
+//     without bank conflicts (lane i of a quarter warp takes row i of an 8-row atom and K32 group
+//     (g0 + i) mod 8).
 //
 // Tile: 128 weight rows (the M side, one TMEM lane per row) x NTOK tokens (the N side) per
 // block, K walked in 256-column super-blocks.  Warp roles:
 //   warp 0      lane 0 issues the raw TMA stream: 4-bit code tiles + metadata (3-D maps over the
-//               split tile layout, no swizzle) and the activations' fp32 scales / int32 sums;
-//               lane 1 issues the int8 activation tiles (2-D map, 128-byte swizzle, rows beyond
-//               m zero-filled) into the operand ring;
-//   warp 1      allocates TMEM; one lane issues the eight K32 MMAs of a super-block, each into
-//               the next accumulator buffer, each followed by tcgen05.commit;
-//   warps 2-5   (2-3 for wide tiles) expand nibbles to int8 in the K-major 128-byte-swizzled operand layout and build
-//               the (a, a', sum, sum') table of the token pairs;
-//   warps 6..   epilogue: thread = weight row; decode that row's six-bit scales once per
-//               super-block, then per K32 group tcgen05.ld its accumulator columns and scale.
-//               Tiles of 64/128 tokens use 8 warps (two column halves per TMEM lane quarter);
-//               tiles of 16/32 tokens (decode) use 16 warps, four per quarter, each taking every
-//               fourth K32 group, and add their sums in warp order at the end of the tile.
+//               split tile layout, no swizzle); lane 1 issues the int8 activation tiles (2-D map,
+//               128-byte swizzle, rows beyond m zero-filled) into the operand ring;
+//   warp 1      allocates TMEM; one lane issues, per K32 group, the constant MMA and the data MMA
+//               into the next accumulator buffer, then tcgen05.commit;
+//   expanders   (6 to 10 warps) expand nibbles to int8 in the K-major 128-byte-swizzled operand
+//               layout, decode the six-bit scales into the row tables (S, -Mn) and build the
+//               (a', a'', a*sum, a*sum') table of the token pairs from the activations' scales and
+//               sums in global memory;
+//   epilogue    per K32 group tcgen05.ld its accumulator patch and scale.  Tiles of 64 / 128
+//               tokens: 16 warps, four column quarters per TMEM lane quarter; narrower tiles
+//               split the eight K32 groups over two warps per lane quarter (and 32-token tiles
+//               the columns in two) and add their sums in warp order at the end of a tile.
 // The kernel is persistent (one block per SM walks the tile list), so TMEM allocation, barrier
 // set-up and pipeline fill are paid once and the loads of the next tile overlap the epilogue of
 // the current one.
@@ -31,14 +51,16 @@
 #include "common.cuh"
 #include "launch.h"
 #include "tma.cuh"
+#include "umma.cuh"
 
 namespace q4k {
 namespace {
 
 constexpr int kRows = 128;
 constexpr int kProducerWarp = 0, kMmaWarp = 1, kFirstExpander = 2;
-constexpr uint32_t kMagicI = 0x4B400000u;   // bit pattern of 1.5 * 2^23
-constexpr float kMagicF = 12582912.0f;
+constexpr uint32_t kPreset = 1u << 17;  // what the constant MMA leaves in every accumulator: 32 * 64 * 64
+constexpr uint32_t kConstByte = 0x40404040u;
+constexpr int kConstBytes = 16 * 1024;  // 128 rows of 128 bytes, the layout of the data operands (every byte equal, so the swizzle is moot)
 
 // NTOK tokens per tile; NCOL <= NTOK accumulator columns actually drained (8 when m <= 8).
 //
@@ -48,49 +70,55 @@ constexpr float kMagicF = 12582912.0f;
 //                freed by the expanders.  Deep for narrow tiles: this is the HBM prefetch.
 //   O (operands) int8 weight tile written by the expanders + int8 activation tile written by
 //                TMA, both in the UMMA K-major 128-byte-swizzled layout; freed by the MMA warp's
-//                tcgen05.commit as soon as the eight MMAs of the super-block have read it.
-//   S (scales)   per-row metadata copy and the (a, a', sum, sum') table; freed by the epilogue.
-// Epilogue warps: every warp may only touch the TMEM lanes of its quarter (warp % 4).  Wide
-// tiles split the columns over two warps per quarter; narrow tiles (decode) interleave the
-// eight K32 groups over kGroupSplit warps per quarter, whose partial sums are added in warp
-// order at the end of a tile.
+//                tcgen05.commit as soon as the MMAs of the super-block have read it.
+//   S (scales)   per-row metadata copy and the activation-scale table; freed by the epilogue.
+// Epilogue warps: every warp may only touch the TMEM lanes of its quarter (warp % 4).
 template <int NTOK, int NCOL> struct Cfg {
-  static constexpr int kColSplit = NTOK >= 64 ? 2 : 1;
-  static constexpr bool kChunked = NTOK >= 64;
-  static constexpr int kGroupSplit = NTOK >= 64 ? 1 : (NTOK >= 32 ? 2 : 4);
+  static constexpr int kColSplit = NTOK >= 64 ? 4 : (NTOK >= 32 ? 2 : 1);
+  static constexpr int kGroupSplit = NTOK >= 64 ? 1 : 2;
   static constexpr int kEpilogueWarps = 4 * kColSplit * kGroupSplit;
-  static constexpr int kExpanders = 4;
+  // Roles are aligned to groups of four warps (the register file is shared by the four warps that sit
+  // on one scheduler each): producer + MMA + expanders fill the first groups, the epilogue the rest.
+  static constexpr int kExpanders = NTOK >= 64 ? 6 : 10;
+  // Wide tiles: the non-epilogue warps give registers back, the epilogue warps take them
+  // (setmaxnreg); 24 warps start at 80 registers each.
+  static constexpr bool kRebalance = NTOK >= 64;
+  static constexpr int kRegsLow = 48, kRegsHigh = 96;  // 8 * 48 + 16 * 96 = 24 * 80: the block's own allocation is the pool
   static constexpr int kFirstEpilogue = kFirstExpander + kExpanders;
   static constexpr int kWarps = kFirstEpilogue + kEpilogueWarps;
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kColsPerWarp = NCOL / kColSplit;
   static constexpr int kAccBufs = (512 / NTOK) > 16 ? 16 : (512 / NTOK);
-  // Narrow tiles: one tcgen05.commit (and one pair of barriers) per four MMAs -- the single
-  // issuing thread is otherwise the bottleneck.
-  static constexpr int kMmaPerCommit = NTOK <= 32 ? 4 : 1;
+  // One tcgen05.commit, one wait and one release per set of two (narrow tiles: four) K32 groups: barrier
+  // traffic is pure overhead next to the arithmetic of a group.
+  static constexpr int kMmaPerCommit = NTOK <= 32 ? 4 : 2;
   static constexpr int kAccSets = kAccBufs / kMmaPerCommit;
   // ring depths
-  static constexpr int kRaw = NTOK <= 16 ? 5 : (NTOK <= 64 ? 4 : 2);
+  static constexpr int kRaw = NTOK <= 16 ? 4 : (NTOK <= 64 ? 3 : 2);
   static constexpr int kOps = 2;
-  static constexpr int kScl = 4;
+  static constexpr int kScl = NTOK >= 128 ? 2 : 3;
   // raw stage
-  static constexpr int kRawCodes = 16 * 1024, kRawMeta = 16 * 128, kRawScale = NTOK * 32;
-  static constexpr int oRawCodes = 0, oRawMeta = kRawCodes, oRawScales = oRawMeta + kRawMeta, oRawSums = oRawScales + kRawScale;
-  static constexpr int kRawStage = (oRawSums + kRawScale + 1023) / 1024 * 1024;
-  static constexpr int kRawTx = kRawCodes + kRawMeta + 2 * kRawScale;
+  static constexpr int kRawCodes = 16 * 1024, kRawMeta = 16 * 128;
+  static constexpr int oRawCodes = 0, oRawMeta = kRawCodes;
+  static constexpr int kRawStage = kRawCodes + kRawMeta;
+  static constexpr int kRawTx = kRawCodes + kRawMeta;
   // operand stage
   static constexpr int kAExp = 2 * kRows * 128, kB = 2 * NTOK * 128;
   static constexpr int oAExp = 0, oB = kAExp;
   static constexpr int kOpStage = (kAExp + kB + 1023) / 1024 * 1024;
   static constexpr int kBTx = kB;
-  // scale stage
-  static constexpr int kAf = 8 * NTOK * 8;
-  static constexpr int oMeta = 0, oAf = kRawMeta;
-  static constexpr int kSclStage = (kRawMeta + kAf + 127) / 128 * 128;
+  // scale stage: row scales S = d * sc * 2^100 ([group][lane quarter][row & 7][row / 8 & 3]) | -dmin (same row order)
+  //              | six-bit mins as bf16 [row][8] | a' = a * 2^49 [group][token] | a * sum as three bf16 terms
+  //              [token][term][group] | stamp of the last stage with an overflowing a'
+  static constexpr int kRowTab = 8 * kRows * 4;
+  static constexpr int oS = 0, oNd = kRowTab, oMt = oNd + kRows * 4, oAf = oMt + kRows * 16, oAsT = oAf + 8 * NTOK * 4,
+                       oWide = oAsT + NTOK * 48;
+  static constexpr int kSclStage = (oWide + 16 + 127) / 128 * 128;
   // whole layout
   static constexpr int oOps = 0;
   static constexpr int oRawRing = oOps + kOps * kOpStage;
-  static constexpr int oSclRing = oRawRing + kRaw * kRawStage;
+  static constexpr int oConst = oRawRing + kRaw * kRawStage;
+  static constexpr int oSclRing = oConst + kConstBytes;
   static constexpr int kRedBytes = kGroupSplit > 1 ? kEpilogueWarps * kColsPerWarp * 32 * 4 : 0;
   static constexpr int oRed = oSclRing + kScl * kSclStage;
   static constexpr int oCtrl = oRed + kRedBytes;
@@ -98,39 +126,20 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kBarriers = 2 * kRaw + 3 * kOps + 2 * kScl + 2 * kAccSets + 1;
   static constexpr int kSmem = oCtrl + kBarriers * 8 + 64 + 1024 /*alignment slack*/;
   static_assert(kSmem <= 227 * 1024, "shared memory budget");
+  static_assert(kOpStage % 1024 == 0 && oRawRing % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
-// K-major, 128-byte swizzle: 8-row atoms of 1024 bytes; version 1; layout type 2.
-__device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
-  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
-         (uint64_t(2) << 61);
-}
-// kind::i8, s8 x s8 -> s32, both operands K-major, M = 128, N = ntok.
-__host__ __device__ constexpr uint32_t umma_idesc(int ntok) {
-  return (2u << 4) | (1u << 7) | (1u << 10) | (uint32_t(ntok >> 3) << 17) | (uint32_t(kRows >> 4) << 24);
-}
-__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc) {
-  asm volatile(
-      "{ .reg .pred p; setp.ne.b32 p, %4, 0;\n"
-      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p; }"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(0), "r"(0) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                 "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-               : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-
 struct TcParams {
-  const float* residual;
-  float* out;
+  const float* xscales;    // activations' fp32 scales [m][G]
+  const int32_t* xsums;    // and int32 sums
+  const float* residual;   // same geometry as the destinations
+  float* out[8];           // fp32 destinations: one buffer, or every rank's copy of a gathered output
+  uint16_t* out_bf16;      // when set, the single destination is bf16 (round to nearest even)
+  uint32_t* peer_flag[8];  // gather only: rank g's arrival counters; [rank] counts this rank's deliveries
+  uint32_t* done;          // gather only: block counter of this launch, zero on entry and on exit
+  uint32_t* unsignalled;   // gather only: finished projections of this rank not yet announced to the peers
+  uint32_t ndst, rank;
+  uint32_t out_stride, out_row0;  // destination element of (token, row) = token * out_stride + out_row0 + row
   int32_t* partials;
   float* partial_tiles;  // split-K scratch [slice][m][n]
   uint32_t* tickets;
@@ -138,10 +147,47 @@ struct TcParams {
   uint32_t n, m, tiles_k, split_k, G, row_tiles, tok_tiles;
 };
 
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
-  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-               : "r"(taddr));
+// Accumulator patch of 16 TMEM lanes x (8 * NB) columns in the MMA C-fragment layout: register
+// 4j + 2i + e of lane l = (lane 8i + l / 4, column 8j + 2 (l % 4) + e) of the patch.
+template <int NB> __device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, uint32_t* r) {
+  static_assert(NB == 1 || NB == 2 || NB == 4, "column blocks per load");
+  if constexpr (NB == 1) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr));
+  } else if constexpr (NB == 2) {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x2.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]) : "r"(taddr));
+  } else {
+    asm volatile("tcgen05.ld.sync.aligned.16x256b.x4.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+  }
+}
+
+__device__ __forceinline__ float2 as_f2(uint32_t x, uint32_t y) { return make_float2(__uint_as_float(x), __uint_as_float(y)); }
+
+// D += A (16 x 16, bf16) * B (16 x 8, bf16), fp32 accumulate: the warp-level tensor-core MMA, used for the min term.
+__device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ float2 lds64f(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts16(uint32_t a, uint16_t x) { asm volatile("st.shared.u16 [%0], %1;" ::"r"(a), "h"(x) : "memory"); }
+
+// Accumulator buffer and barrier parity of K32 group g of the block's it-th super-block (buffers are used round
+// robin, eight per super-block): compile-time for the four-buffer tiles when g is.
+template <int AB> __device__ __forceinline__ void acc_slot(uint32_t it, uint32_t g, uint32_t& b, uint32_t& parity) {
+  static_assert(AB == 4 || AB == 8 || AB == 16, "accumulator buffers");
+  if constexpr (AB == 4) { b = g & 3; parity = (g >> 2) & 1; }
+  else if constexpr (AB == 8) { b = g; parity = it & 1; }
+  else { b = ((it & 1) << 3) + g; parity = (it >> 1) & 1; }
 }
 
 // Persistent: block b walks tiles b, b + gridDim.x, ...; a tile is (row tile of 128 rows,
@@ -150,8 +196,7 @@ __device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
 template <int NTOK, int NCOL, bool Dump>
 __global__ void __launch_bounds__(Cfg<NTOK, NCOL>::kThreads, 1)
 mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_constant__ CUtensorMap tm_meta,
-                   const __grid_constant__ CUtensorMap tm_act, const __grid_constant__ CUtensorMap tm_scales,
-                   const __grid_constant__ CUtensorMap tm_sums, TcParams p) {
+                   const __grid_constant__ CUtensorMap tm_act, const TcParams p) {
   using C = Cfg<NTOK, NCOL>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* const smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -164,6 +209,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
 
   uint32_t const warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint32_t const num_tiles = p.row_tiles * p.tok_tiles * p.split_k;
+  uint32_t const smem_s = smem_u32(smem);
 
   uint32_t const bar0 = smem_u32(bars);
   auto bar_raw_full = [&](uint32_t i) { return bar0 + 8 * i; };
@@ -185,19 +231,22 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       mbar_init(bar_op_free(i), 1);
     }
     for (uint32_t i = 0; i < C::kScl; ++i) { mbar_init(bar_s_full(i), C::kExpanders); mbar_init(bar_s_free(i), C::kEpilogueWarps); }
-    for (uint32_t i = 0; i < C::kAccSets; ++i) { mbar_init(bar_acc_full(i), 1); mbar_init(bar_acc_empty(i), 4 * C::kColSplit * C::kMmaPerCommit); }
+    for (uint32_t i = 0; i < C::kAccSets; ++i) { mbar_init(bar_acc_full(i), 1); mbar_init(bar_acc_empty(i), C::kEpilogueWarps); }
     mbar_init(bar_ep, C::kEpilogueWarps);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-  if (warp == kMmaWarp) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], 512;" ::"r"(smem_u32(tmem_slot)) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-  }
+  // The constant operand: every byte 64.
+  for (uint32_t i = threadIdx.x; i < kConstBytes / 4; i += C::kThreads) reinterpret_cast<uint32_t*>(smem + C::oConst)[i] = kConstByte;
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == kMmaWarp) tmem_alloc_all(smem_u32(tmem_slot));
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   uint32_t const tmem_base = *tmem_slot;
+  // Row-sharded use: the projections that finished before this launch are announced to the peers now (their
+  // grids have completed, so their stores into the peers' buffers are visible).
+  if (p.done != nullptr && blockIdx.x == 0 && threadIdx.x == 0) announce_deliveries(p.unsignalled, p.peer_flag, p.ndst, p.rank);
 
   auto tile_coords = [&](uint32_t t, uint32_t& row_tile, uint32_t& tok_tile, uint32_t& slice, uint32_t& kb0, uint32_t& kb1) {
     tok_tile = t % p.tok_tiles;  // token tile fastest: blocks running together share weight tiles in L2
@@ -218,6 +267,11 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     }
   };
 
+  if (warp < C::kFirstEpilogue) {
+  if constexpr (C::kRebalance) {
+    static_assert(C::kFirstEpilogue % 4 == 0 && C::kWarps == 24, "register split assumes 8 + 16 warps");
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsLow));
+  }
   if (warp == kProducerWarp) {
     // Raw stream: code tiles, metadata, activation scales and sums of every super-block.
     if (lane == 0) {
@@ -226,17 +280,15 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
         uint32_t row_tile, tok_tile, slice, kb0, kb1;
         tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
-        int const rg0 = int(row_tile * (kRows / 8)), tok0 = int(tok_tile * NTOK);
+        int const rg0 = int(row_tile * (kRows / 8));
         for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
           uint32_t const r = it % C::kRaw, use = it / C::kRaw;
-          if (!mbar_wait(bar_raw_free(r), (use & 1) ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
+          if (!mbar_wait_inline<2048, 256>(bar_raw_free(r), (use & 1) ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
           uint8_t* const st = smem + C::oRawRing + r * C::kRawStage;
           uint32_t const bar = bar_raw_full(r);
           mbar_expect_tx(bar, C::kRawTx);
           tma_3d(smem_u32(st + C::oRawCodes), &tm_codes, 0, int(kb), rg0, bar);
           tma_3d(smem_u32(st + C::oRawMeta), &tm_meta, 0, int(kb), rg0, bar);
-          tma_2d(smem_u32(st + C::oRawScales), &tm_scales, int(kb) * 8, tok0, bar);
-          tma_2d(smem_u32(st + C::oRawSums), &tm_sums, int(kb) * 8, tok0, bar);
         }
       }
       if (*abort_flag) drain(it > C::kRaw ? it - C::kRaw : 0, it, C::kRaw, bar_raw_full(0));
@@ -251,7 +303,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         int const tok0 = int(tok_tile * NTOK);
         for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
           uint32_t const o = it % C::kOps, use = it / C::kOps;
-          if (!mbar_wait(bar_op_free(o), (use & 1) ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
+          if (!mbar_wait_inline<1024, 256>(bar_op_free(o), (use & 1) ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
           uint8_t* const st = smem + C::oOps + o * C::kOpStage;
           uint32_t const bar = bar_b_full(o);
           mbar_expect_tx(bar, C::kBTx);
@@ -263,7 +315,8 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
-      constexpr uint32_t idesc = umma_idesc(NTOK);
+      constexpr uint32_t idesc = umma_idesc_i8(NTOK);
+      uint64_t const cdesc = umma_desc_sw128(smem_u32(smem + C::oConst));
       uint32_t it = 0;
       bool ok = true;
       for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
@@ -271,71 +324,122 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
         for (uint32_t kb = kb0; ok && kb < kb1; ++kb, ++it) {
           uint32_t const o = it % C::kOps, use = it / C::kOps;
-          if (!mbar_wait(bar_b_full(o), use & 1, abort_flag, p.status, 3)) { ok = false; break; }
-          if (!mbar_wait(bar_op_ready(o), use & 1, abort_flag, p.status, 4)) { ok = false; break; }
+          if (!mbar_wait_inline(bar_b_full(o), use & 1, abort_flag, p.status, 3)) { ok = false; break; }
+          if (!mbar_wait_inline(bar_op_ready(o), use & 1, abort_flag, p.status, 4)) { ok = false; break; }
           tc_fence_after();
           uint8_t* const st = smem + C::oOps + o * C::kOpStage;
           uint32_t const a_base = smem_u32(st + C::oAExp), b_base = smem_u32(st + C::oB);
 #pragma unroll
           for (uint32_t g = 0; g < 8; ++g) {
-            uint32_t const i = it * 8 + g, b = i % C::kAccBufs, round = i / C::kAccBufs, set = b / C::kMmaPerCommit;
+            uint32_t b, parity;
+            acc_slot<C::kAccBufs>(it, g, b, parity);
+            uint32_t const set = b / C::kMmaPerCommit;
             if (g % C::kMmaPerCommit == 0) {
-              if (!mbar_wait(bar_acc_empty(set), (round & 1) ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
+              if (!mbar_wait_inline<256, 64>(bar_acc_empty(set), parity ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
               tc_fence_after();
             }
-            uint64_t const ad = umma_desc(a_base + (g >> 2) * (kRows * 128) + (g & 3) * 32);
-            uint64_t const bd = umma_desc(b_base + (g >> 2) * (NTOK * 128) + (g & 3) * 32);
-            umma_i8(tmem_base + b * NTOK, ad, bd, idesc);
+            uint64_t const ad = umma_desc_sw128(a_base + (g >> 2) * (kRows * 128) + (g & 3) * 32);
+            uint64_t const bd = umma_desc_sw128(b_base + (g >> 2) * (NTOK * 128) + (g & 3) * 32);
+            umma_i8(tmem_base + b * NTOK, cdesc, cdesc, idesc, 0);  // every accumulator = 2^17
+            umma_i8(tmem_base + b * NTOK, ad, bd, idesc, 1);        // += the K32 dots
             if (g % C::kMmaPerCommit == C::kMmaPerCommit - 1) umma_commit(bar_acc_full(set));
           }
           if (ok) umma_commit(bar_op_free(o));  // operands are free once these MMAs have read them
         }
       }
     }
-  } else if (warp < C::kFirstEpilogue) {
+  } else {
     uint32_t const et = threadIdx.x - kFirstExpander * 32;  // 0 .. 32*kExpanders-1
+    constexpr uint32_t kET = C::kExpanders * 32;
+    constexpr uint32_t kEntries = (NTOK * 8 + kET - 1) / kET;  // activation-table entries per thread
     uint32_t it = 0;
     bool ok = true;
     for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
       uint32_t row_tile, tok_tile, slice, kb0, kb1;
       tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
+      uint32_t const tok0 = tok_tile * NTOK;
       for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
         uint32_t const r = it % C::kRaw, o = it % C::kOps, sc = it % C::kScl;
-        if (!mbar_wait(bar_raw_full(r), (it / C::kRaw) & 1, abort_flag, p.status, 6)) { ok = false; break; }
-        if (!mbar_wait(bar_op_free(o), ((it / C::kOps) & 1) ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
-        if (!mbar_wait(bar_s_free(sc), ((it / C::kScl) & 1) ^ 1, abort_flag, p.status, 8)) { ok = false; break; }
-        const uint8_t* const raw = smem + C::oRawRing + r * C::kRawStage;
-        uint8_t* const ops = smem + C::oOps + o * C::kOpStage;
-        uint8_t* const scl = smem + C::oSclRing + sc * C::kSclStage;
-        // 1024 raw 16-byte chunks: chunk q = (row q/8 of the tile, K32 group q%8).
-#pragma unroll 2
-        for (uint32_t q = et; q < 1024; q += C::kExpanders * 32) {
-          uint32_t const R = q >> 3, g = q & 7, r7 = R & 7;
-          uint4 const w = *reinterpret_cast<const uint4*>(raw + C::oRawCodes + q * 16);
-          uint32_t const ww[4] = {w.x, w.y, w.z, w.w};
-          uint32_t ov[8];
+        // The activations' scales and sums of this super-block come straight from global memory (they sit in
+        // L2); the loads are in flight while the nibbles are expanded.
+        float av[kEntries];
+        int sv[kEntries];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t const lo = ww[i] & 0x0f0f0f0fu, hi = (ww[i] >> 4) & 0x0f0f0f0fu;
-            ov[2 * i] = __byte_perm(lo, hi, 0x5140);      // columns 8i .. 8i+3
-            ov[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // columns 8i+4 .. 8i+7
-          }
-          uint8_t* const dst = ops + C::oAExp + (g >> 2) * (kRows * 128) + (R >> 3) * 1024 + r7 * 128;
-          uint32_t const c = (g & 3) * 2;
-          *reinterpret_cast<uint4*>(dst + ((c ^ r7) << 4)) = make_uint4(ov[0], ov[1], ov[2], ov[3]);
-          *reinterpret_cast<uint4*>(dst + (((c + 1) ^ r7) << 4)) = make_uint4(ov[4], ov[5], ov[6], ov[7]);
+        for (uint32_t e = 0; e < kEntries; ++e) {
+          uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
+          bool const live = j < NTOK * 8 && tok0 + tk < p.m;
+          size_t const idx = size_t(tok0 + tk) * p.G + kb * 8 + g;
+          av[e] = live ? __ldg(p.xscales + idx) : 0.f;
+          sv[e] = live ? __ldg(p.xsums + idx) : 0;
         }
-        // Metadata rows (16 bytes each) move to the scale ring; the epilogue reads them there.
-        for (uint32_t j = et; j < kRows; j += C::kExpanders * 32)
-          *reinterpret_cast<uint4*>(scl + C::oMeta + j * 16) = *reinterpret_cast<const uint4*>(raw + C::oRawMeta + j * 16);
-        // (a, a', float(sum), float(sum')) per K32 group and token pair.
-        for (uint32_t j = et; j < NTOK * 8; j += C::kExpanders * 32) {
-          uint32_t const tk = j >> 3, g = j & 7;
-          float const a = *reinterpret_cast<const float*>(raw + C::oRawScales + j * 4);
-          float const fs = float(*reinterpret_cast<const int*>(raw + C::oRawSums + j * 4));
-          float* const dst = reinterpret_cast<float*>(scl + C::oAf + (g * (NTOK / 2) + (tk >> 1)) * 16) + (tk & 1);
-          dst[0] = a;
-          dst[2] = fs;
+        if (!mbar_wait_inline<1024, 128>(bar_raw_full(r), (it / C::kRaw) & 1, abort_flag, p.status, 6)) { ok = false; break; }
+        if (!mbar_wait_inline<1024, 128>(bar_op_free(o), ((it / C::kOps) & 1) ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
+        if (!mbar_wait_inline<1024, 128>(bar_s_free(sc), ((it / C::kScl) & 1) ^ 1, abort_flag, p.status, 8)) { ok = false; break; }
+        uint32_t const raw = smem_s + C::oRawRing + r * C::kRawStage;
+        uint32_t const ops = smem_s + C::oOps + o * C::kOpStage;
+        uint32_t const scl = smem_s + C::oSclRing + sc * C::kSclStage;
+        // 1024 raw 16-byte chunks = (row of the tile, K32 group).  A quarter warp takes the eight rows of one
+        // 8-row atom, lane i the row i and the group (g0 + i) mod 8: its eight reads and each of its two sets of
+        // eight writes fall into eight different 16-byte bank groups.
+        {
+          uint32_t const i8 = et & 7;
+#pragma unroll 2
+          for (uint32_t oc = et >> 3; oc < 128; oc += kET / 8) {
+            uint32_t const atom = oc >> 3, g = ((oc & 7) + i8) & 7, R = atom * 8 + i8;
+            uint4 const w = lds128(raw + C::oRawCodes + (R * 8 + g) * 16);
+            uint32_t const ww[4] = {w.x, w.y, w.z, w.w};
+            uint32_t ov[8];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t const lo = ww[i] & 0x0f0f0f0fu, hi = (ww[i] >> 4) & 0x0f0f0f0fu;
+              ov[2 * i] = __byte_perm(lo, hi, 0x5140);      // columns 8i .. 8i+3
+              ov[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // columns 8i+4 .. 8i+7
+            }
+            uint32_t const dst = ops + C::oAExp + (g >> 2) * (kRows * 128) + atom * 1024 + i8 * 128;
+            uint32_t const c = (g & 3) * 2;
+            sts128(dst + ((c ^ i8) << 4), ov[0], ov[1], ov[2], ov[3]);
+            sts128(dst + (((c + 1) ^ i8) << 4), ov[4], ov[5], ov[6], ov[7]);
+          }
+        }
+        // Row tables: S = d * sc * 2^100 of every (row, group) and -dmin of every row, laid out so that an epilogue
+        // lane finds its four rows (l/4, +8, +16, +24 of its lane quarter) in one 16-byte word; the six-bit mins
+        // as bf16, one 16-byte row each (the A operand of the min-term MMA).
+        for (uint32_t row = et; row < kRows; row += kET) {
+          uint4 const cm = lds128(raw + C::oRawMeta + row * 16);
+          float const d100 = fp16_bits_to_f32(cm.x & 0xffffu) * 0x1p100f, ndmin = -fp16_bits_to_f32(cm.x >> 16);
+          ScaleMinWords const sm = decode_scale_min(cm.y, cm.z, cm.w);
+          uint32_t const slot = (row >> 5) * 32 + (row & 7) * 4 + ((row >> 3) & 3);
+          uint32_t const st = scl + C::oS + slot * 4;
+          uint32_t mb[4];
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            uint32_t const scw = g < 4 ? sm.sc_lo : sm.sc_hi, mnw = g < 4 ? sm.mn_lo : sm.mn_hi;
+            sts32f(st + g * kRows * 4, d100 * float(byte_of(scw, g & 3)));
+            uint32_t const mbits = __float_as_uint(float(byte_of(mnw, g & 3))) >> 16;  // a six-bit integer is exact in bf16
+            if (g & 1) mb[g >> 1] |= mbits << 16; else mb[g >> 1] = mbits;
+          }
+          sts128(scl + C::oMt + row * 16, mb[0], mb[1], mb[2], mb[3]);
+          sts32f(scl + C::oNd + slot * 4, ndmin);
+        }
+        // Activation tables: a' = a * 2^49 per (group, token), and a * sum split into three bf16 terms that add up to
+        // it exactly (the B operand of the min-term MMA).  A scale so large that a' is not finite stamps the stage,
+        // and the epilogue then works from the plain scales.
+#pragma unroll
+        for (uint32_t e = 0; e < kEntries; ++e) {
+          uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
+          if (j < NTOK * 8) {
+            sts32f(scl + C::oAf + (g * NTOK + tk) * 4, av[e] * 0x1p49f);
+            float const as = av[e] * float(sv[e]);
+            uint16_t const t0 = f32_to_bf16_rne(as);
+            float const r1 = as - bf16_bits_to_f32(t0);
+            uint16_t const t1 = f32_to_bf16_rne(r1);
+            uint16_t const t2 = f32_to_bf16_rne(r1 - bf16_bits_to_f32(t1));
+            uint32_t const dst = scl + C::oAsT + tk * 48 + g * 2;
+            sts16(dst, t0);
+            sts16(dst + 16, t1);
+            sts16(dst + 32, t2);
+            if (av[e] > 0x1p78f) atomicMax(reinterpret_cast<uint32_t*>(smem + C::oSclRing + sc * C::kSclStage + C::oWide), it + 1);
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's async proxy
         __syncwarp();
@@ -346,104 +450,163 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         }
       }
     }
+  }
   } else {
-    constexpr int GS = C::kGroupSplit, CW = C::kColsPerWarp, CH = CW >= 16 ? 16 : 8;
+    if constexpr (C::kRebalance) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(C::kRegsHigh));
+    constexpr int GS = C::kGroupSplit, CW = C::kColsPerWarp, NB = CW / 8;
     uint32_t const ep = warp - C::kFirstEpilogue, quarter = warp & 3;  // TMEM lanes 32*quarter ..
     uint32_t const u = ep >> 2, cs = u % C::kColSplit, gs = u / C::kColSplit;
     uint32_t const col0 = cs * CW;
-    uint32_t const my_row = quarter * 32 + lane;  // row inside the tile
+    uint32_t const q = lane & 3, R0 = lane >> 2;
+    // This thread's values: v = ((h * NB + j) * 2 + i) * 2 + e  <->  row 32*quarter + 16h + 8i + R0 of the tile,
+    // token col0 + 8j + 2q + e of the tile.
     bool const final_warp = gs == 0;               // holds the tile's sums after the group-split reduction
     uint32_t it = 0, ep_phase = 0;
     bool ok = true;
     auto ep_sync = [&](int code) {  // all epilogue warps meet (bounded like every other wait)
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ep);
-      if (!mbar_wait(bar_ep, ep_phase, abort_flag, p.status, code)) ok = false;
+      if (!mbar_wait_inline(bar_ep, ep_phase, abort_flag, p.status, code)) ok = false;
       ep_phase ^= 1;
     };
+    // The accumulator patches are read one half (16 TMEM lanes) at a time into two register buffers, and the read of
+    // the next half -- of the same group, of this warp's next group, or of the next super-block's first -- is always
+    // in flight while the current half is folded: tcgen05.ld has a latency of several hundred cycles, and four
+    // epilogue warps per scheduler cannot hide it by themselves.
+    uint32_t const lane_base = tmem_base + ((quarter * 32u) << 16) + col0;
+    uint32_t rA[4 * NB], rB[4 * NB];
+    constexpr int PER = C::kMmaPerCommit / GS;  // groups of this warp per accumulator set
+    auto fetch_first_half = [&](uint32_t it2, uint32_t g2, bool wait_set) -> bool {  // group g2 of super-block it2 into rA
+      uint32_t b2, parity2;
+      acc_slot<C::kAccBufs>(it2, g2, b2, parity2);
+      if (wait_set) {
+        if (!mbar_wait_inline<512, 128>(bar_acc_full(b2 / C::kMmaPerCommit), parity2, abort_flag, p.status, 10)) return false;
+        tc_fence_after();
+      }
+      tmem_ld_frag<NB>(lane_base + b2 * NTOK, rA);
+      return true;
+    };
+    if (blockIdx.x < num_tiles) ok = fetch_first_half(0, gs, true);
     for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
       uint32_t row_tile, tok_tile, slice, kb0, kb1;
       tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
-      uint32_t const row0 = row_tile * kRows, tok0 = tok_tile * NTOK;
-      float2 acc[CW / 2];
+      uint32_t const row0 = row_tile * kRows + quarter * 32 + R0, tok0 = tok_tile * NTOK + col0 + 2 * q;
+      float2 acc[2][NB][2];
 #pragma unroll
-      for (int i = 0; i < CW / 2; ++i) acc[i] = make_float2(0.f, 0.f);
+      for (int h = 0; h < 2; ++h)
+#pragma unroll
+        for (int j = 0; j < NB; ++j) acc[h][j][0] = acc[h][j][1] = make_float2(0.f, 0.f);
 
       for (uint32_t kb = kb0; ok && kb < kb1; ++kb, ++it) {
         uint32_t const sc = it % C::kScl;
-        if (!mbar_wait(bar_s_full(sc), (it / C::kScl) & 1, abort_flag, p.status, 9)) { ok = false; break; }
-        const uint8_t* const scl = smem + C::oSclRing + sc * C::kSclStage;
-        // This row's metadata: d, dmin and eight six-bit (scale, min) pairs.
-        uint4 const cm = *reinterpret_cast<const uint4*>(scl + C::oMeta + my_row * 16);
-        float const d = fp16_bits_to_f32(cm.x & 0xffffu), ndmin = -fp16_bits_to_f32(cm.x >> 16);
-        ScaleMinWords const sm = decode_scale_min(cm.y, cm.z, cm.w);
-#pragma unroll(NTOK >= 64 ? 8 : 2)
-        for (int tt = 0; tt < 8 / GS; ++tt) {
+        bool const has_next = kb + 1 < kb1 || t + gridDim.x < num_tiles;
+        if (!mbar_wait_inline<512, 128>(bar_s_full(sc), (it / C::kScl) & 1, abort_flag, p.status, 9)) { ok = false; break; }
+        uint32_t const scl = smem_s + C::oSclRing + sc * C::kSclStage;
+        bool const wide = lds32(scl + C::oWide) == it + 1;
+        uint32_t const stab = scl + C::oS + (quarter * 8 + R0) * 16;
+        // ---- min term of the whole super-block on the tensor cores: rows x groups (six-bit mins, bf16) times
+        // groups x tokens (a * sum in three bf16 terms; products exact, fp32 accumulation), scaled by -dmin.
+        // (Where the groups are split over several warps, the first of them adds it.)
+        if (GS == 1 || gs == 0) {
+          uint32_t const mrow = scl + C::oMt + (quarter * 32 + R0) * 16 + q * 4;
+          uint32_t const am00 = lds32(mrow), am01 = lds32(mrow + 8 * 16), am10 = lds32(mrow + 16 * 16), am11 = lds32(mrow + 24 * 16);
+          float4 const nd4 = lds128f(scl + C::oNd + (quarter * 8 + R0) * 16);
+          float const nd[4] = {nd4.x, nd4.y, nd4.z, nd4.w};
+#pragma unroll
+          for (int j = 0; j < NB; ++j) {
+            uint32_t const brow = scl + C::oAsT + (col0 + 8 * j + R0) * 48 + q * 4;
+            uint32_t const b0 = lds32(brow), b1 = lds32(brow + 16), b2 = lds32(brow + 32);
+            float m0[4] = {0.f, 0.f, 0.f, 0.f}, m1[4] = {0.f, 0.f, 0.f, 0.f};
+            mma_bf16(m0, am00, am01, am00, am01, b2, 0u);
+            mma_bf16(m1, am10, am11, am10, am11, b2, 0u);
+            mma_bf16(m0, am00, am01, am00, am01, b0, b1);
+            mma_bf16(m1, am10, am11, am10, am11, b0, b1);
+#pragma unroll
+            for (int i2 = 0; i2 < 2; ++i2) {
+              acc[0][j][i2] = __ffma2_rn(make_float2(nd[i2], nd[i2]), make_float2(m0[2 * i2], m0[2 * i2 + 1]), acc[0][j][i2]);
+              acc[1][j][i2] = __ffma2_rn(make_float2(nd[2 + i2], nd[2 + i2]), make_float2(m1[2 * i2], m1[2 * i2 + 1]), acc[1][j][i2]);
+            }
+          }
+        }
+        // One trip per accumulator set (PER groups of this warp), unrolled inside: what depends on the position in
+        // the set is decided at compile time, and the code stays small enough not to spill.
+#pragma unroll 1
+        for (int ts = 0; ts < 8 / GS / PER; ++ts) {
+#pragma unroll
+        for (int tu = 0; tu < PER; ++tu) {
+          int const tt = ts * PER + tu;
           uint32_t const g = gs + GS * tt;
-          uint32_t const scw = (g < 4) ? sm.sc_lo : sm.sc_hi, mnw = (g < 4) ? sm.mn_lo : sm.mn_hi;
-          uint32_t const sh = (g & 3) * 8;
-          // six-bit integers to fp32 through the 1.5 * 2^23 bias: stays off the conversion pipe
-          float const D = d * (__uint_as_float(kMagicI | ((scw >> sh) & 0xffu)) - kMagicF);
-          float const nMn = ndmin * (__uint_as_float(kMagicI | ((mnw >> sh) & 0xffu)) - kMagicF);
-          float const cD = -kMagicF * D;  // exact: D has at most 17 significant bits
-          float2 const D2 = make_float2(D, D), cD2 = make_float2(cD, cD), nMn2 = make_float2(nMn, nMn);
-          uint32_t const i = it * 8 + g, b = i % C::kAccBufs, round = i / C::kAccBufs, set = b / C::kMmaPerCommit;
-          if (!mbar_wait(bar_acc_full(set), round & 1, abort_flag, p.status, 10)) { ok = false; break; }
-          tc_fence_after();
-          uint32_t const taddr = tmem_base + ((quarter * 32u) << 16) + b * NTOK + col0;
-          const float4* const afp = reinterpret_cast<const float4*>(scl + C::oAf + (g * (NTOK / 2) + col0 / 2) * 16);
-          uint32_t r[CW];
-          if constexpr (C::kChunked) {
-            // Wide tiles: read and fold 16 columns at a time; with the group loop unrolled the
-            // compiler overlaps one chunk's arithmetic with the next chunk's TMEM read.
+          bool const last_of_set = tu == PER - 1;
+          // S and c = -S * 2^-132 (= -D * 2^-32, exact) of this lane's four rows
+          float4 const S4 = lds128f(stab + g * (kRows * 4));
+          float2 const k2 = make_float2(-0x1p-132f, -0x1p-132f);
+          float2 const c01 = __fmul2_rn(make_float2(S4.x, S4.y), k2), c23 = __fmul2_rn(make_float2(S4.z, S4.w), k2);
+          float const Sr[4] = {S4.x, S4.y, S4.z, S4.w}, cr[4] = {c01.x, c01.y, c23.x, c23.y};
+          uint32_t const afp = scl + C::oAf + (g * NTOK + col0 + 2 * q) * 4;
+          float2 f[NB];  // a' of tokens col0 + 8j + 2q, + 1
 #pragma unroll
-            for (int cc = 0; cc < CW; cc += 16) {
-              tmem_ld16(taddr + cc, r + cc);
-              tmem_wait_ld();
-              if (cc + 16 >= CW) {
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(bar_acc_empty(set));
+          for (int j = 0; j < NB; ++j) f[j] = lds64f(afp + 32 * j);
+          if (wide) {  // plain scales from global memory; the products below then carry the 2^49 themselves
+#pragma unroll
+            for (int j = 0; j < NB; ++j) {
+              uint32_t const tk = tok0 + 8 * j;
+              f[j].x = tk < p.m ? p.xscales[size_t(tk) * p.G + kb * 8 + g] : 0.f;
+              f[j].y = tk + 1 < p.m ? p.xscales[size_t(tk + 1) * p.G + kb * 8 + g] : 0.f;
+            }
+          }
+          uint32_t b, parity;
+          acc_slot<C::kAccBufs>(it, g, b, parity);
+          auto fold = [&](const uint32_t (&r)[4 * NB], int h) {
+            if (!wide) {
+#pragma unroll
+              for (int j = 0; j < NB; ++j) {
+#pragma unroll
+                for (int i2 = 0; i2 < 2; ++i2) {
+                  int const k = 2 * h + i2;
+                  float2 const v = __ffma2_rn(as_f2(r[4 * j + 2 * i2], r[4 * j + 2 * i2 + 1]), make_float2(Sr[k], Sr[k]), make_float2(cr[k], cr[k]));  // D * P * 2^-49
+                  acc[h][j][i2] = __ffma2_rn(f[j], v, acc[h][j][i2]);                                                   // + a * (D * P)
+                }
               }
+            } else {
 #pragma unroll
-              for (int j = cc; j < cc + 16; j += 2) {
-                float4 const f = afp[j / 2];
-                float2 const pf = make_float2(__uint_as_float(r[j] + kMagicI), __uint_as_float(r[j + 1] + kMagicI));
-                float2 v = __ffma2_rn(pf, D2, cD2);
-                v = __ffma2_rn(nMn2, make_float2(f.z, f.w), v);
-                acc[j / 2] = __ffma2_rn(make_float2(f.x, f.y), v, acc[j / 2]);
+              for (int j = 0; j < NB; ++j) {
+#pragma unroll
+                for (int i2 = 0; i2 < 2; ++i2) {
+                  int const k = 2 * h + i2;
+                  float2 v = __ffma2_rn(as_f2(r[4 * j + 2 * i2], r[4 * j + 2 * i2 + 1]), make_float2(Sr[k], Sr[k]), make_float2(cr[k], cr[k]));
+                  v = __fmul2_rn(v, make_float2(0x1p49f, 0x1p49f));
+                  acc[h][j][i2] = __ffma2_rn(f[j], v, acc[h][j][i2]);
+                }
               }
             }
-          } else {
-            // Narrow tiles: all TMEM reads of the group go out before the single wait, and the
-            // buffer returns to the MMA warp before the arithmetic.
+            if (Dump) {
 #pragma unroll
-            for (int cc = 0; cc < CW; cc += CH) {
-              if constexpr (CH == 16) tmem_ld16(taddr + cc, r + cc);
-              else tmem_ld8(taddr + cc, r + cc);
+              for (int v = 0; v < 4 * NB; ++v) {
+                uint32_t const row = row0 + 16 * h + 8 * ((v >> 1) & 1), token = tok0 + 8 * (v >> 2) + (v & 1);
+                if (row < p.n && token < p.m)
+                  p.partials[(uint64_t(token) * p.n + row) * p.G + kb * 8 + g] = int32_t(r[v] - kPreset);
+              }
             }
-            tmem_wait_ld();
+          };
+          // first half: in rA; the second half of the same group goes out before it is folded
+          tmem_wait_ld();
+          tmem_ld_frag<NB>(lane_base + (16u << 16) + b * NTOK, rB);
+          fold(rA, 0);
+          // second half: in rB; with it the warp has read all it wants of this group
+          tmem_wait_ld();
+          if (last_of_set) {  // the set goes back to the MMA warp
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty(set));
-#pragma unroll
-            for (int j = 0; j < CW; j += 2) {
-              float4 const f = afp[j / 2];  // (a, a', sum, sum') of tokens col0+j, col0+j+1
-              float2 const pf = make_float2(__uint_as_float(r[j] + kMagicI), __uint_as_float(r[j + 1] + kMagicI));
-              float2 v = __ffma2_rn(pf, D2, cD2);                     // D * float(P), one rounding
-              v = __ffma2_rn(nMn2, make_float2(f.z, f.w), v);         // - Mn * float(sum)
-              acc[j / 2] = __ffma2_rn(make_float2(f.x, f.y), v, acc[j / 2]);
-            }
+            if (lane == 0) mbar_arrive(bar_acc_empty(b / C::kMmaPerCommit));
           }
-          if (Dump) {
-            uint32_t const row = row0 + my_row;
-#pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              uint32_t const token = tok0 + col0 + j;
-              if (row < p.n && token < p.m)
-                p.partials[(uint64_t(token) * p.n + row) * p.G + kb * 8 + g] = int32_t(r[j]);
-            }
+          if (tt + 1 < 8 / GS) {
+            if (!fetch_first_half(it, g + GS, last_of_set)) { ok = false; break; }
+          } else if (has_next) {
+            if (!fetch_first_half(it + 1, gs, true)) { ok = false; break; }
           }
+          fold(rB, 1);
+        }
+        if (!ok) break;
         }
         if (!ok) break;
         __syncwarp();
@@ -452,43 +615,52 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       if (!ok) break;
 
       // ---- end of tile: combine the group-split warps, then write (or hand to the split-K fix-up)
+      auto value = [&](int v) -> float& {
+        float2& a2 = acc[v / (4 * NB)][(v / 4) % NB][(v >> 1) & 1];
+        return (v & 1) ? a2.y : a2.x;
+      };
+      auto row_of = [&](int v) { return row0 + 16 * (v / (4 * NB)) + 8 * ((v >> 1) & 1); };
+      auto token_of = [&](int v) { return tok0 + 8 * ((v / 4) % NB) + (v & 1); };
       if constexpr (GS > 1) {
 #pragma unroll
-        for (int j = 0; j < CW; ++j) red[(ep * CW + j) * 32 + lane] = (j & 1) ? acc[j / 2].y : acc[j / 2].x;
+        for (int v = 0; v < CW; ++v) red[(ep * CW + v) * 32 + lane] = value(v);
         ep_sync(11);
         if (!ok) break;
         if (final_warp) {
 #pragma unroll
-          for (int j = 0; j < CW; ++j) {
-            float v = 0.f;
+          for (int v = 0; v < CW; ++v) {
+            float sum = 0.f;
 #pragma unroll
-            for (int k2 = 0; k2 < GS; ++k2) v += red[((ep + 4 * C::kColSplit * k2) * CW + j) * 32 + lane];  // warp order
-            if (j & 1) acc[j / 2].y = v; else acc[j / 2].x = v;
+            for (int k2 = 0; k2 < GS; ++k2) sum += red[((ep + 4 * C::kColSplit * k2) * CW + v) * 32 + lane];  // warp order
+            value(v) = sum;
           }
         }
       }
-      uint32_t const row = row0 + my_row;
-      bool const writer = final_warp && row < p.n;
-      if (p.split_k == 1) {
-        if (writer) {
+      auto store = [&](uint32_t token, uint32_t row, float v) {
+        uint64_t const o = uint64_t(token) * p.out_stride + p.out_row0 + row;
+        if (p.residual) v += p.residual[o];
+        if (p.out_bf16) {
+          p.out_bf16[o] = f32_to_bf16_rne(v);
+        } else {
+          p.out[0][o] = v;
 #pragma unroll
-          for (int j = 0; j < CW; ++j) {
-            uint32_t const token = tok0 + col0 + j;
-            if (token < p.m) {
-              uint64_t const o = uint64_t(token) * p.n + row;
-              p.out[o] = ((j & 1) ? acc[j / 2].y : acc[j / 2].x) + (p.residual ? p.residual[o] : 0.f);
-            }
-          }
+          for (int g2 = 1; g2 < 8; ++g2)
+            if (g2 < int(p.ndst)) p.out[g2][o] = v;
+        }
+      };
+      if (p.split_k == 1) {
+        if (final_warp) {
+#pragma unroll
+          for (int v = 0; v < CW; ++v)
+            if (row_of(v) < p.n && token_of(v) < p.m) store(token_of(v), row_of(v), value(v));
         }
       } else {
         uint64_t const plane = uint64_t(p.m) * p.n;
-        if (writer) {
+        if (final_warp) {
 #pragma unroll
-          for (int j = 0; j < CW; ++j) {
-            uint32_t const token = tok0 + col0 + j;
-            if (token < p.m)
-              __stcg(p.partial_tiles + slice * plane + uint64_t(token) * p.n + row, (j & 1) ? acc[j / 2].y : acc[j / 2].x);
-          }
+          for (int v = 0; v < CW; ++v)
+            if (row_of(v) < p.n && token_of(v) < p.m)
+              __stcg(p.partial_tiles + slice * plane + uint64_t(token_of(v)) * p.n + row_of(v), value(v));
         }
         __threadfence();
         ep_sync(12);
@@ -504,15 +676,14 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         if (!ok) break;
         if (*last_flag) {
           __threadfence();
-          if (writer) {
+          if (final_warp) {
 #pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              uint32_t const token = tok0 + col0 + j;
-              if (token < p.m) {
-                uint64_t const o = uint64_t(token) * p.n + row;
-                float v = 0.f;
-                for (uint32_t s2 = 0; s2 < p.split_k; ++s2) v += __ldcg(p.partial_tiles + s2 * plane + o);  // slice order
-                p.out[o] = v + (p.residual ? p.residual[o] : 0.f);
+            for (int v = 0; v < CW; ++v) {
+              if (row_of(v) < p.n && token_of(v) < p.m) {
+                uint64_t const o = uint64_t(token_of(v)) * p.n + row_of(v);
+                float sum = 0.f;
+                for (uint32_t s2 = 0; s2 < p.split_k; ++s2) sum += __ldcg(p.partial_tiles + s2 * plane + o);  // slice order
+                store(token_of(v), row_of(v), sum);
               }
             }
           }
@@ -526,21 +697,32 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     }
   }
 
-  // Teardown: everyone meets, TMEM goes back.
+  // Teardown: everyone meets (a read of TMEM still in flight after an early exit lands first), TMEM goes back.
+  if (warp >= C::kFirstEpilogue) tmem_wait_ld();
   tc_fence_before();
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, 512;" ::"r"(tmem_base) : "memory");
+    tmem_dealloc_all(tmem_base);
+  }
+  // Row-sharded use: the last block of the grid records one more finished projection.  It is announced to the
+  // peers by the next kernel of the stream, once this grid has completed and its peer stores are visible.
+  if (p.done != nullptr && threadIdx.x == 0) {
+    __threadfence();
+    uint32_t const old = atomicAdd(p.done, 1u);
+    if (old == gridDim.x - 1) {
+      *p.done = 0;
+      if (*reinterpret_cast<volatile int*>(p.status) == 0) atomicAdd(p.unsignalled, 1u);
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------------
 template <int NTOK, int NCOL>
-cudaError_t launch_ntok(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
+cudaError_t launch_ntok(const WeightView& w, const Q8View& x, const TcOutput& o, int32_t* partials,
                         uint32_t split_k, float* partial_tiles, uint32_t* tickets, int* status, cudaStream_t stream) {
   using C = Cfg<NTOK, NCOL>;
-  CUtensorMap tm_codes, tm_meta, tm_act, tm_scales, tm_sums;
+  CUtensorMap tm_codes, tm_meta, tm_act;
   uint64_t const rgs = w.padded_n / 8, G = x.padded_k / 32;
   {
     uint64_t dims[3] = {256, w.tiles_k, rgs}, strides[2] = {1024, uint64_t(w.tiles_k) * 1024};
@@ -560,25 +742,22 @@ cudaError_t launch_ntok(const WeightView& w, const Q8View& x, float* out, const 
     if (!make_map(&tm_act, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, x.codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
       return cudaErrorInvalidValue;
   }
-  {
-    uint64_t dims[2] = {G, x.m}, strides[1] = {G * 4};
-    uint32_t box[2] = {8, NTOK};
-    if (!make_map(&tm_scales, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, x.scales, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
-      return cudaErrorInvalidValue;
-    if (!make_map(&tm_sums, CU_TENSOR_MAP_DATA_TYPE_INT32, 2, x.sums, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
-      return cudaErrorInvalidValue;
-  }
   auto kernel = partials ? mmq_tcgen05_kernel<NTOK, NCOL, true> : mmq_tcgen05_kernel<NTOK, NCOL, false>;
   cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmem);
   if (st != cudaSuccess) return st;
   uint32_t const row_tiles = (w.padded_n + kRows - 1) / kRows, tok_tiles = (x.m + NTOK - 1) / NTOK;
-  TcParams p{residual, out, partials, partial_tiles, tickets, status, w.n, x.m, w.tiles_k, split_k, uint32_t(G), row_tiles, tok_tiles};
+  TcParams p{};
+  p.xscales = x.scales; p.xsums = x.sums;
+  p.residual = o.residual;
+  for (uint32_t g = 0; g < 8; ++g) p.peer_flag[g] = g < o.ndst ? o.flags[g] : nullptr;
+  p.done = o.done; p.unsignalled = o.unsignalled; p.rank = o.rank;
+  for (uint32_t g = 0; g < 8; ++g) p.out[g] = g < o.ndst ? o.out[g] : nullptr;
+  p.out_bf16 = o.out_bf16; p.ndst = o.ndst; p.out_stride = o.stride ? o.stride : w.n; p.out_row0 = o.row0;
+  p.partials = partials; p.partial_tiles = partial_tiles; p.tickets = tickets; p.status = status;
+  p.n = w.n; p.m = x.m; p.tiles_k = w.tiles_k; p.split_k = split_k; p.G = uint32_t(G); p.row_tiles = row_tiles; p.tok_tiles = tok_tiles;
   uint64_t const tiles = uint64_t(row_tiles) * tok_tiles * split_k;
-  // Narrow (decode) tiles: one persistent block per SM walks the tile list.  Wide tiles run one
-  // block per tile; measured faster there (the hardware scheduler balances the long tiles).
-  uint32_t grid = uint32_t(tiles);
-  if (NTOK <= 32 && tiles > uint64_t(sm_count())) grid = uint32_t(sm_count());
-  kernel<<<grid, C::kThreads, C::kSmem, stream>>>(tm_codes, tm_meta, tm_act, tm_scales, tm_sums, p);
+  uint32_t const grid = uint32_t(tiles < uint64_t(sm_count()) ? tiles : uint64_t(sm_count()));
+  kernel<<<grid, C::kThreads, C::kSmem, stream>>>(tm_codes, tm_meta, tm_act, p);
   return cudaGetLastError();
 }
 
@@ -619,17 +798,17 @@ TcPlan plan_tcgen05(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_r
   return p;
 }
 
-cudaError_t launch_mmq_tcgen05(const WeightView& w, const Q8View& x, float* out, const float* residual,
-                               int32_t* partials, const TcPlan& plan, void* partial_tiles, uint32_t* tickets,
-                               int* status, cudaStream_t stream) {
+cudaError_t launch_mmq_tcgen05(const WeightView& w, const Q8View& x, const TcOutput& out, int32_t* partials,
+                               const TcPlan& plan, void* partial_tiles, uint32_t* tickets, int* status, cudaStream_t stream) {
   float* pt = static_cast<float*>(partial_tiles);
+  if (out.ndst < 1 || out.ndst > 8 || (out.out_bf16 ? out.ndst != 1 : out.out[0] == nullptr)) return cudaErrorInvalidValue;
   switch (plan.ntok) {
     case 16:
-      if (x.m <= 8) return launch_ntok<16, 8>(w, x, out, residual, partials, plan.split_k, pt, tickets, status, stream);
-      return launch_ntok<16, 16>(w, x, out, residual, partials, plan.split_k, pt, tickets, status, stream);
-    case 32: return launch_ntok<32, 32>(w, x, out, residual, partials, plan.split_k, pt, tickets, status, stream);
-    case 64: return launch_ntok<64, 64>(w, x, out, residual, partials, plan.split_k, pt, tickets, status, stream);
-    case 128: return launch_ntok<128, 128>(w, x, out, residual, partials, plan.split_k, pt, tickets, status, stream);
+      if (x.m <= 8) return launch_ntok<16, 8>(w, x, out, partials, plan.split_k, pt, tickets, status, stream);
+      return launch_ntok<16, 16>(w, x, out, partials, plan.split_k, pt, tickets, status, stream);
+    case 32: return launch_ntok<32, 32>(w, x, out, partials, plan.split_k, pt, tickets, status, stream);
+    case 64: return launch_ntok<64, 64>(w, x, out, partials, plan.split_k, pt, tickets, status, stream);
+    case 128: return launch_ntok<128, 128>(w, x, out, partials, plan.split_k, pt, tickets, status, stream);
     default: return cudaErrorInvalidValue;
   }
 }

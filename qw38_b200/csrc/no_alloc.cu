@@ -46,11 +46,6 @@ int scratch_for_current_device(unsigned char** out) {
   return Q4K_OK;
 }
 
-bool overlap(const void* a, uint64_t an, const void* b, uint64_t bn) {
-  auto x = reinterpret_cast<uintptr_t>(a), y = reinterpret_cast<uintptr_t>(b);
-  return x < y + bn && y < x + an;
-}
-
 }  // namespace
 
 extern "C" int q4k_q8_project_static(const q4k_weight* w, q4k_q8_input x, float* output, uint64_t output_len,
@@ -67,14 +62,17 @@ extern "C" int q4k_q8_project_static(const q4k_weight* w, q4k_q8_input x, float*
       x.codes_len != uint64_t(x.m) * x.padded_k || x.scales_len != x.codes_len / 32 || x.sums_len != x.scales_len ||
       output_len != uint64_t(x.m) * w->n || (residual_len != 0 && (residual_len != output_len || !residual)))
     return q4k::set_error(Q4K_ERR_INVALID_ARGUMENT, "static: invalid geometry");
-  if (reinterpret_cast<uintptr_t>(w->codes) % 4 || reinterpret_cast<uintptr_t>(w->scales) % 2 ||
-      reinterpret_cast<uintptr_t>(x.codes) % 4 || reinterpret_cast<uintptr_t>(output) % 4)
-    return q4k::set_error(Q4K_ERR_INVALID_ARGUMENT, "static: misaligned operand");
-  if (overlap(output, output_len * 4, w->codes, w->codes_bytes) || overlap(output, output_len * 4, w->scales, w->scales_bytes) ||
-      overlap(output, output_len * 4, x.codes, x.codes_len) || overlap(output, output_len * 4, x.scales, x.scales_len * 4) ||
-      overlap(output, output_len * 4, x.sums, x.sums_len * 4) ||
-      (residual_len && overlap(output, output_len * 4, residual, residual_len * 4)))
-    return q4k::set_error(Q4K_ERR_INVALID_ARGUMENT, "static: output overlaps an input");
+  // The checks of the allocating entry (no allocation is involved in them): every operand aligned, device
+  // memory of the current device, inside one allocation, and the live operands pairwise disjoint -- a host
+  // pointer is rejected here instead of faulting on the GPU.
+  q4k::Operand operands[7] = {{w->codes, w->codes_bytes, 4, "weight.codes"},
+                              {w->scales, w->scales_bytes, 2, "weight.scales"},
+                              {x.codes, x.codes_len, 4, "input.codes"},
+                              {x.scales, x.scales_len * 4, 4, "input.scales"},
+                              {x.sums, x.sums_len * 4, 4, "input.sums"},
+                              {output, output_len * 4, 4, "output"},
+                              {residual, residual_len * 4, 4, "residual"}};
+  if (int st = q4k::check_operands(operands, residual_len ? 7 : 6)) return st;
 
   q4k::WeightView wv{static_cast<const uint8_t*>(w->codes), static_cast<const uint8_t*>(w->scales), w->n, w->padded_n,
                      w->padded_k / 256};

@@ -27,8 +27,8 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
-// Slow path of a bounded wait, kept out of line so that the wait sites stay a single try.
-static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+// Slow path of a bounded wait.
+__device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   long long const t0 = clock64();
   for (uint32_t spin = 0;; ++spin) {
     if (mbar_try(bar, parity)) return true;
@@ -42,11 +42,63 @@ static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity
     }
   }
 }
+// The same, kept out of line so that the wait sites stay a single try.
+static __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  return mbar_wait_spin(bar, parity, abort_flag, status, code);
+}
 // Bounded wait for the phase with the given parity.  False = gave up (abort raised).
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
+// Bounded wait for kernels in which many warps wait at once next to warps that compute: a waiting warp must not
+// take issue slots from the working ones, so between two tries it sleeps (FirstNs, doubling up to MaxNs) instead
+// of spinning; the abort flag and the clock are looked at every eighth try.  Fully inlined: a function call inside
+// a kernel that moves registers between warps with setmaxnreg does not compile.
+template <uint32_t MaxNs = 256, uint32_t FirstNs = 32>
+__device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
+  if (mbar_try(bar, parity)) return true;
+  long long const t0 = clock64();
+  uint32_t ns = FirstNs;
+  for (uint32_t tries = 1;; ++tries) {
+    __nanosleep(ns);
+    if (mbar_try(bar, parity)) return true;
+    if (ns < MaxNs) ns *= 2;
+    if ((tries & 7u) == 0) {
+      if (*abort_flag) return false;
+      if (clock64() - t0 > kWaitCycles) {
+        *abort_flag = 1;
+        atomicExch(status, code);
+        return false;
+      }
+    }
+  }
+}
+
+// Shared-memory accesses by 32-bit shared-space address (generic pointers into the dynamic buffer cost 64-bit
+// address arithmetic and generic loads on every access).
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ float4 lds128f(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1];" : "=r"(v) : "r"(a));
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t a, uint32_t x, uint32_t y, uint32_t z, uint32_t w) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(a), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+__device__ __forceinline__ void sts128f(uint32_t a, float x, float y, float z, float w) {
+  asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
+}
+__device__ __forceinline__ void sts32f(uint32_t a, float x) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(x) : "memory"); }
 
 __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
