@@ -422,8 +422,9 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
       return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: every rank needs a 4-byte aligned output and flag array");
   if ((residual_len != 0 && residual_len != uint64_t(x.m) * desc->total_rows) || (residual_len != 0 && !residual))
     return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: residual must cover m x total_rows");
-  if (!q4k::gemv_tma_supported(view(w), view(x)))
-    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: needs m <= 16 and 16-byte aligned weight shards");
+  bool const narrow = x.m <= q4k::kGemvTmaMaxTokens;
+  if (narrow ? !q4k::gemv_tma_supported(view(w), view(x)) : !q4k::tcgen05_supported(view(w), view(x)))
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project_gather: needs 16-byte aligned weight shards and activations");
   // Peer mappings cannot be checked against this device's allocations; the local operands are.
   Region regions[5] = {{w.codes, w.codes_bytes, 4, "shard.codes"},
                        {w.scales, w.scales_bytes, 2, "shard.scales"},
@@ -431,23 +432,42 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
                        {x.scales, x.scales_len * 4, 4, "input.scales"},
                        {x.sums, x.sums_len * 4, 4, "input.sums"}};
   if (int st = check_distinct(regions, 5, false)) return st;
-  q4k::GemvTmaPlan plan = q4k::plan_gemv_tma(x.m, w.n, w.padded_k / 256, 0, 0);
-  uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
-  void* scratch = nullptr;
-  if (int st = own_scratch(partial_bytes, &scratch, stream)) return st;
-  uint8_t* const base = static_cast<uint8_t*>(scratch);
   int* const status = q4k::kernel_status_word();
   if (!status) return Q4K_ERR_STATUS;
-  q4k::GemvTmaGather gather{};
-  for (uint32_t g = 0; g < desc->ranks; ++g) { gather.outputs[g] = desc->outputs[g]; gather.flags[g] = desc->flags[g]; }
   // words 8 and 9 of this rank's own flag array: its unannounced projections and the block counter
-  gather.unsignalled = desc->flags[desc->rank] + 8;
-  gather.done = desc->flags[desc->rank] + 9;
-  gather.ranks = desc->ranks; gather.rank = desc->rank; gather.row_offset = desc->row_offset; gather.total_rows = desc->total_rows;
-  Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), nullptr, residual_len ? residual : nullptr, nullptr, plan,
-                                base + kTicketRegion, reinterpret_cast<uint32_t*>(base),
-                                status, stream, &gather),
-           "q4k_q8.gemv_tma_gather");
+  uint32_t* const unsignalled = desc->flags[desc->rank] + 8;
+  uint32_t* const done = desc->flags[desc->rank] + 9;
+  void* scratch = nullptr;
+  if (narrow) {
+    q4k::GemvTmaPlan plan = q4k::plan_gemv_tma(x.m, w.n, w.padded_k / 256, 0, 0);
+    uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
+    if (int st = own_scratch(partial_bytes, &scratch, stream)) return st;
+    uint8_t* const base = static_cast<uint8_t*>(scratch);
+    q4k::GemvTmaGather gather{};
+    for (uint32_t g = 0; g < desc->ranks; ++g) { gather.outputs[g] = desc->outputs[g]; gather.flags[g] = desc->flags[g]; }
+    gather.unsignalled = unsignalled;
+    gather.done = done;
+    gather.ranks = desc->ranks; gather.rank = desc->rank; gather.row_offset = desc->row_offset; gather.total_rows = desc->total_rows;
+    Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), nullptr, residual_len ? residual : nullptr, nullptr, plan,
+                                  base + kTicketRegion, reinterpret_cast<uint32_t*>(base), status, stream, &gather),
+             "q4k_q8.gemv_tma_gather");
+    return Q4K_OK;
+  }
+  // More than sixteen tokens: the tcgen05 kernel, whose writer stores into every rank's buffer the same way.
+  q4k::TcPlan plan = q4k::plan_tcgen05(x.m, w.n, w.padded_k / 256, 0);
+  uint64_t const tiles = uint64_t((w.padded_n + 127) / 128) * ((x.m + plan.ntok - 1) / plan.ntok);
+  if (plan.split_k > 1 && tiles * 4 > kTicketRegion - 64) plan.split_k = 1;
+  uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * x.m * w.n * 4 : 0;
+  if (int st = own_scratch(partial_bytes, &scratch, stream)) return st;
+  uint8_t* const base = static_cast<uint8_t*>(scratch);
+  q4k::TcOutput out{};
+  for (uint32_t g = 0; g < desc->ranks; ++g) { out.out[g] = desc->outputs[g]; out.flags[g] = desc->flags[g]; }
+  out.residual = residual_len ? residual : nullptr;
+  out.ndst = desc->ranks; out.stride = desc->total_rows; out.row0 = desc->row_offset;
+  out.done = done; out.unsignalled = unsignalled; out.rank = desc->rank;
+  Q4K_CUDA(q4k::launch_mmq_tcgen05(view(w), view(x), out, nullptr, plan, base + kTicketRegion, reinterpret_cast<uint32_t*>(base),
+                                   status, stream),
+           "q4k_q8.mmq_tcgen05_gather");
   return Q4K_OK;
 }
 

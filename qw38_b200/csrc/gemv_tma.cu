@@ -425,7 +425,8 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       uint32_t const old = atomicAdd(p.done, 1u);
       if (old == gridDim.x - 1) {
         *p.done = 0;
-        if (!*abort_flag) atomicAdd(p.unsignalled, 1u);
+        // counted only if no block of any launch so far gave up a wait (the status word is shared by all blocks)
+        if (!*abort_flag && *reinterpret_cast<volatile int*>(p.status) == 0) atomicAdd(p.unsignalled, 1u);
       }
     }
   }

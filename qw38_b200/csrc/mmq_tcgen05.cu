@@ -74,7 +74,7 @@ constexpr int kConstBytes = 16 * 1024;  // 128 rows of 128 bytes, the layout of 
 //   S (scales)   per-row metadata copy and the activation-scale table; freed by the epilogue.
 // Epilogue warps: every warp may only touch the TMEM lanes of its quarter (warp % 4).
 template <int NTOK, int NCOL> struct Cfg {
-  static constexpr int kColSplit = NTOK >= 64 ? 4 : (NTOK >= 32 ? 2 : 1);
+  static constexpr int kColSplit = NTOK >= 128 ? 4 : (NTOK >= 64 ? 2 : (NTOK >= 32 ? 2 : 1));
   static constexpr int kGroupSplit = NTOK >= 64 ? 1 : 2;
   static constexpr int kEpilogueWarps = 4 * kColSplit * kGroupSplit;
   // Roles are aligned to groups of four warps (the register file is shared by the four warps that sit
@@ -82,7 +82,7 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kExpanders = NTOK >= 64 ? 6 : 10;
   // Wide tiles: the non-epilogue warps give registers back, the epilogue warps take them
   // (setmaxnreg); 24 warps start at 80 registers each.
-  static constexpr bool kRebalance = NTOK >= 64;
+  static constexpr bool kRebalance = NTOK >= 128;
   static constexpr int kRegsLow = 48, kRegsHigh = 96;  // 8 * 48 + 16 * 96 = 24 * 80: the block's own allocation is the pool
   static constexpr int kFirstEpilogue = kFirstExpander + kExpanders;
   static constexpr int kWarps = kFirstEpilogue + kEpilogueWarps;
@@ -677,15 +677,22 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         if (*last_flag) {
           __threadfence();
           if (final_warp) {
+            // Slices are added in slice order; all of a slice's values are requested before any is used, so the
+            // reads of a slice are in flight together (one memory latency per slice, not per value).
+            float sum[CW];
 #pragma unroll
-            for (int v = 0; v < CW; ++v) {
-              if (row_of(v) < p.n && token_of(v) < p.m) {
-                uint64_t const o = uint64_t(token_of(v)) * p.n + row_of(v);
-                float sum = 0.f;
-                for (uint32_t s2 = 0; s2 < p.split_k; ++s2) sum += __ldcg(p.partial_tiles + s2 * plane + o);  // slice order
-                store(token_of(v), row_of(v), sum);
-              }
+            for (int v = 0; v < CW; ++v) sum[v] = 0.f;
+            for (uint32_t s2 = 0; s2 < p.split_k; ++s2) {
+              float part[CW];
+#pragma unroll
+              for (int v = 0; v < CW; ++v)
+                part[v] = (row_of(v) < p.n && token_of(v) < p.m) ? __ldcg(p.partial_tiles + s2 * plane + uint64_t(token_of(v)) * p.n + row_of(v)) : 0.f;
+#pragma unroll
+              for (int v = 0; v < CW; ++v) sum[v] += part[v];
             }
+#pragma unroll
+            for (int v = 0; v < CW; ++v)
+              if (row_of(v) < p.n && token_of(v) < p.m) store(token_of(v), row_of(v), sum[v]);
           }
         }
       }
@@ -776,20 +783,19 @@ TcPlan plan_tcgen05(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_r
   uint32_t const blocks = ((n + 7) / 8 * 8 + kRows - 1) / kRows * ((m + p.ntok - 1) / p.ntok);
   uint32_t split = split_k_request;
   if (split == 0) {
-    // Pick the K split whose tile count fills whole rounds of the machine best, among splits
-    // that leave at least four super-blocks per slice.  Every extra slice costs a partial tile
-    // of m*n fp32 written and read back, which is negligible for a handful of tokens and
-    // prohibitive for a prefill chunk -- the penalty grows with m.
+    // Pick the K split with the shortest estimated time, in units of one super-block step of a block: a block
+    // pays its pipeline fill once, and per tile the K walk plus the tile end (longer with split-K: partial tiles
+    // go through global scratch and the last block of a tile adds them).  Measured on 64-token tiles: fill ~1.7,
+    // tile end ~1, split-K tile end ~2.5 steps.  Slices keep at least four super-blocks.
     uint32_t const sms = uint32_t(sm_count());
     uint32_t const max_split = tiles_k / 4 ? (tiles_k / 4 > 16 ? 16 : tiles_k / 4) : 1;
-    double const penalty = 0.01 + 0.1 * (m >= 128 ? 1.0 : double(m) / 128.0);
-    double best = -1.0;
+    double best = 1e30;
     split = 1;
     for (uint32_t s = 1; s <= max_split; ++s) {
       uint64_t const tiles = uint64_t(blocks) * s;
       uint64_t const rounds = (tiles + sms - 1) / sms;
-      double eff = double(tiles) / double(rounds * sms) - penalty * (s - 1);
-      if (eff > best + 1e-9) { best = eff; split = s; }
+      double const cost = 1.7 + double(rounds) * ((s > 1 ? 2.5 : 1.0) + double((tiles_k + s - 1) / s));
+      if (cost < best - 1e-9) { best = cost; split = s; }
     }
   }
   if (split > tiles_k) split = tiles_k;

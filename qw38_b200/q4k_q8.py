@@ -167,6 +167,12 @@ def q4k_q8_project(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor
     return out
 
 
+def reserve_scratch(partial_bytes: int, stream=None) -> None:
+    """Grow the library-owned split-K scratch of the current device to hold `partial_bytes` of partial tiles
+    (q4k_reserve_scratch): once per device, before a graph is captured whose calls need that much."""
+    _check(L.load().q4k_reserve_scratch(int(partial_bytes), _stream(stream)))
+
+
 def q4k_q8_project_static(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor] = None,
                           residual: Optional[torch.Tensor] = None, *, split_k: int = 0, stream=None) -> torch.Tensor:
     """The projection for callers that may not allocate device memory: split-K scratch lives in a
@@ -363,19 +369,6 @@ def dequantize_bf16(weight: PrefillWeight, stream=None) -> torch.Tensor:
     out = torch.empty((weight.n, weight.k), dtype=torch.bfloat16, device=weight.codes.device)
     _check(L.load().q4k_dequantize_bf16(C.byref(weight.c_struct()), _ptr(out), out.numel(), _stream(stream)))
     return out
-
-
-def prefill_project_bf16(weight: PrefillWeight, x: torch.Tensor, weight_bf16: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """The reference's OTHER prefill route (PrefillDispatch's BF16 path, cuda/prefill.cu:329-335,510-560):
-    unpack the Q4_K weight to bf16 and multiply by the bf16 activations in a library GEMM with fp32
-    accumulation.  x: bfloat16 [m, k]; returns bfloat16 [m, n].  The weights are bit-identical to
-    dequantize_to_bf16; the result is NOT the Q8 equation (activations are not quantised), so it is held
-    to the tolerance of the reference's BF16 path, not to the integer contract.  Pass weight_bf16 (from
-    dequantize_bf16) to reuse the unpacked weight across calls."""
-    if x.dtype != torch.bfloat16 or x.dim() != 2 or x.shape[1] != weight.k:
-        raise Q4KError(L.ERR_INVALID_ARGUMENT, "prefill_project_bf16 takes bfloat16 [m, k] activations")
-    wb = dequantize_bf16(weight) if weight_bf16 is None else weight_bf16
-    return torch.matmul(x, wb.t())
 
 
 def unpack_logical(weight: PrefillWeight, stream=None):
