@@ -236,6 +236,8 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
+  // The stamps of the scale stages start at zero (a stage is stamped with its super-block number + 1).
+  if (threadIdx.x < C::kScl) *reinterpret_cast<uint32_t*>(smem + C::oSclRing + threadIdx.x * C::kSclStage + C::oWide) = 0u;
   // The constant operand: every byte 64.
   for (uint32_t i = threadIdx.x; i < kConstBytes / 4; i += C::kThreads) reinterpret_cast<uint32_t*>(smem + C::oConst)[i] = kConstByte;
   asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
