@@ -174,6 +174,29 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
 int q4k_peer_wait(const q4k_gather_desc* desc, uint64_t limit_cycles, void* stream);
 int q4k_peer_announce(const q4k_gather_desc* desc, void* stream);
 
+/* Profiler ranges: when enabled for the calling thread (default off, as the reference's profiling::enabled,
+ * src/runtime/profiling.hpp:9), q4k_pack_q8_*, q4k_q8_project* and the stages of q4k_q8_mlp run inside NVTX ranges
+ * named like the reference's ("qw38:op name=q4k_project m=.. n=.. k=.. role=.. residual=.. compute=integer_dp4a|
+ * integer_mma", "qw38:op name=q8_pack ..", "..hidden_rms_q8_pack..", "..swiglu_q8_pack..";
+ * cuda/q4k_q8.cu:299-302,326,383, cuda/activation.cu:543), so that traces of the two engines can be compared. */
+void q4k_set_profiling_ranges(int enabled);
+int q4k_get_profiling_ranges(void);
+
+/* Session: the scratch and the failure flag that the reference's entry points find in their engine or runtime
+ * session (cuda/prefill.hpp:72-117 PrefillEngine owns its workspace; src/runtime/session owns the decode
+ * workspace), for callers that want the reference's call signatures without a workspace argument.  Allocates
+ * workspace_bytes (256-byte aligned) plus one zeroed failure flag on the current device; destroy frees them (after
+ * the work that uses them has completed).  q4k_session_take_failure synchronises the stream, returns
+ * Q4K_ERR_INVALID_ARGUMENT ("nonfinite producer ...") if a quantiser flagged non-finite data since the last call,
+ * and clears the flag. */
+typedef struct q4k_session q4k_session;
+int q4k_session_create(uint64_t workspace_bytes, q4k_session** out);
+void q4k_session_destroy(q4k_session* session);
+void* q4k_session_workspace(const q4k_session* session);
+uint64_t q4k_session_workspace_bytes(const q4k_session* session);
+int* q4k_session_failure(const q4k_session* session);
+int q4k_session_take_failure(q4k_session* session, void* stream);
+
 /* Programmatic dependent launch for the decode path (no counterpart in the reference, which
  * replays its decode step as a CUDA graph of fully serialised kernels, src/runtime/language_model.cpp:324-356).
  * When enabled (process-wide, default off), q4k_pack_q8_*, and q4k_q8_project* for m <= 16 launch

@@ -60,6 +60,14 @@ SIGNATURES = {
     "q4k_kernel_status": (_i, [C.POINTER(_i)]),
     "q4k_reserve_scratch": (_i, [_u64, _vp]),
     "q4k_measure_int8_peak": (_i, [_u32, C.POINTER(C.c_double), C.POINTER(C.c_double), _vp]),
+    "q4k_set_profiling_ranges": (None, [_i]),
+    "q4k_get_profiling_ranges": (_i, []),
+    "q4k_session_create": (_i, [_u64, C.POINTER(_vp)]),
+    "q4k_session_destroy": (None, [_vp]),
+    "q4k_session_workspace": (_vp, [_vp]),
+    "q4k_session_workspace_bytes": (_u64, [_vp]),
+    "q4k_session_failure": (_vp, [_vp]),
+    "q4k_session_take_failure": (_i, [_vp, _vp]),
     "q4k_set_launch_overlap": (None, [_i]),
     "q4k_get_launch_overlap": (_i, []),
     "q4k_pad_n": (_u64, [_u32]),

@@ -16,6 +16,8 @@
 #include <mutex>
 #include <vector>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "../../include/q4k_b200.h"
 #include "launch.h"
 
@@ -41,6 +43,29 @@ int fail_cuda(cudaError_t st, const char* op) {
     cudaError_t st__ = (expr);                              \
     if (st__ != cudaSuccess) return fail_cuda(st__, op);    \
   } while (0)
+
+// Profiler ranges with the reference's strings (src/runtime/profiling.hpp, cuda/q4k_q8.cu:299-302,326,383), opt-in
+// per thread like the reference's, so that traces of the two engines line up.
+thread_local bool g_ranges = false;
+class ScopedRange {
+ public:
+  template <class... Args>
+  explicit ScopedRange(char const* format, Args... args) noexcept : active_(g_ranges) {
+    if (active_) {
+      char name[384];
+      std::snprintf(name, sizeof name, format, args...);
+      nvtxRangePushA(name);
+    }
+  }
+  ~ScopedRange() {
+    if (active_) nvtxRangePop();
+  }
+  ScopedRange(ScopedRange const&) = delete;
+  ScopedRange& operator=(ScopedRange const&) = delete;
+
+ private:
+  bool active_;
+};
 
 using MemGetAddressRange = CUresult (*)(CUdeviceptr*, size_t*, CUdeviceptr);
 MemGetAddressRange address_range_fn() {
@@ -197,7 +222,7 @@ constexpr uint32_t kFlagTrustedSpans = 1u;
 
 int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output, uint64_t output_len,
                  const float* residual, uint64_t residual_len, const q4k_project_options* opt,
-                 cudaStream_t stream, bool residual_in_place = false) {
+                 cudaStream_t stream, bool residual_in_place = false, char const* role = "projection") {
   if (int st = valid_weight(weight, "weight")) return st;
   const q4k_weight& w = *weight;
   if (!valid_input(x) || x.k != w.k || output_len != uint64_t(x.m) * w.n ||
@@ -235,6 +260,8 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
     else kernel = q4k::tcgen05_supported(view(w), view(x)) ? Q4K_KERNEL_TCGEN05 : Q4K_KERNEL_MMA;
   }
   const float* res = residual_len ? residual : nullptr;
+  ScopedRange range("qw38:op name=q4k_project m=%u n=%u k=%u role=%s residual=%u compute=%s", unsigned(x.m), unsigned(w.n),
+                    unsigned(w.k), role, unsigned(res != nullptr), kernel == Q4K_KERNEL_GEMV_DP4A ? "integer_dp4a" : "integer_mma");
   if (kernel == Q4K_KERNEL_GEMV_DP4A) {
     if (x.m > q4k::kGemvDp4aMaxTokens) return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.project: dp4a kernel takes m <= 4");
     Q4K_CUDA(q4k::launch_gemv_dp4a(view(w), view(x), output, res, partials, stream), "q4k_q8.gemv_dp4a");
@@ -323,6 +350,7 @@ int pack_impl(const void* input, bool fp32, uint64_t input_len, const q4k_q8_inp
                        {x.sums, x.sums_len * 4, 4, "output.sums"},
                        {failure, 4, 4, "failure"}};
   if (int st = check_distinct(regions, 5, false)) return st;
+  ScopedRange range("qw38:op name=q8_pack m=%u n=%u k=%u", unsigned(x.m), unsigned(x.k), 1u);
   Q4K_CUDA(q4k::launch_pack_q8(input, fp32, out_view(x), x.k, failure, stream), "q8.pack");
   return Q4K_OK;
 }
@@ -371,6 +399,9 @@ extern "C" {
 const char* q4k_last_error(void) { return g_error; }
 int q4k_last_cuda_status(void) { return g_cuda_status; }
 uint32_t q4k_abi_version(void) { return 1; }
+
+void q4k_set_profiling_ranges(int enabled) { g_ranges = enabled != 0; }
+int q4k_get_profiling_ranges(void) { return g_ranges ? 1 : 0; }
 
 void q4k_set_launch_overlap(int enabled) { g_launch_overlap.store(enabled != 0, std::memory_order_relaxed); }
 int q4k_get_launch_overlap(void) { return g_launch_overlap.load(std::memory_order_relaxed) ? 1 : 0; }
@@ -588,6 +619,73 @@ int decode_one(const q4k_decode_desc& d, const q4k_q8_input& q8, float* rows, cu
   }
 }
 
+// One launch for up to three descriptors that share the (already quantised) input: every weight's rows, its bf16 /
+// fp32 store or residual add, or -- swiglu -- bf16(SiLU(a) * b) of a gate / up pair, all inside the TMA decode kernel
+// (the reference applies these epilogues inside its decode kernels too, cuda/decode_mmv.cu:182-250,619-677).
+// *fused = false when the operands do not qualify (more than 16 rows, unaligned weights, another activation policy);
+// the caller then composes separate launches.
+int decode_fused(const q4k_decode_desc* const* descs, uint32_t count, bool swiglu, const q4k_q8_input& q8, cudaStream_t stream,
+                 bool* fused) {
+  *fused = false;
+  q4k::WeightView ws[3];
+  q4k::GemvTmaOutput outs[3] = {};
+  Region regions[16];
+  int nreg = 0;
+  regions[nreg++] = {q8.codes, q8.codes_len, 4, "input.codes"};
+  regions[nreg++] = {q8.scales, q8.scales_len * 4, 4, "input.scales"};
+  regions[nreg++] = {q8.sums, q8.sums_len * 4, 4, "input.sums"};
+  uint64_t n_total = 0, tiles = 0;
+  for (uint32_t i = 0; i < count; ++i) {
+    const q4k_decode_desc& d = *descs[i];
+    if (d.activation_policy != Q4K_ACTIVATION_Q8_K32 || d.m > q4k::kGemvTmaMaxTokens || d.weight.k != descs[0]->weight.k) return Q4K_OK;
+    ws[i] = view(d.weight);
+    if (!q4k::gemv_tma_supported(ws[i], view(q8))) return Q4K_OK;
+    uint64_t const cells = uint64_t(d.m) * d.weight.n;
+    regions[nreg++] = {d.weight.codes, d.weight.codes_bytes, 4, "weight.codes"};
+    regions[nreg++] = {d.weight.scales, d.weight.scales_bytes, 2, "weight.scales"};
+    switch (d.epilogue) {
+      case Q4K_EPILOGUE_STORE_FP32:
+        outs[i].out = static_cast<float*>(d.output);
+        regions[nreg++] = {d.output, cells * 4, 4, "output"};
+        break;
+      case Q4K_EPILOGUE_STORE_BF16:
+        outs[i].out_bf16 = static_cast<uint16_t*>(d.output);
+        regions[nreg++] = {d.output, cells * 2, 2, "output"};
+        break;
+      case Q4K_EPILOGUE_RESIDUAL_ADD_FP32:
+        outs[i].residual = d.residual;
+        outs[i].out = d.output ? static_cast<float*>(d.output) : const_cast<float*>(d.residual);
+        regions[nreg++] = {d.residual, cells * 4, 4, "residual"};
+        if (d.output && d.output != d.residual) regions[nreg++] = {d.output, cells * 4, 4, "output"};
+        break;
+      case Q4K_EPILOGUE_SWIGLU_STORE_BF16:
+        if (!swiglu) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: SwiGLU epilogue requires paired gate/up launch");
+        if (i == 0) {
+          outs[0].out_bf16 = static_cast<uint16_t*>(d.output);
+          regions[nreg++] = {d.output, cells * 2, 2, "output"};
+        }
+        break;
+      default:
+        return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: unknown epilogue");
+    }
+    n_total += d.weight.n;
+    tiles += (d.weight.padded_n + 15) / 16;
+  }
+  if (int st = check_distinct(regions, nreg, false)) return st;
+  q4k::GemvTmaPlan plan = q4k::plan_gemv_tma_tiles(q8.m, uint32_t(tiles), ws[0].tiles_k, 0, 0, swiglu);
+  uint64_t const partial_bytes = plan.split_k > 1 ? uint64_t(plan.split_k) * q8.m * n_total * 4 : 0;
+  void* scratch = nullptr;
+  if (int st = own_scratch(partial_bytes, &scratch, stream)) return st;
+  int* const status = q4k::kernel_status_word();
+  if (!status) return Q4K_ERR_STATUS;
+  uint8_t* const base = static_cast<uint8_t*>(scratch);
+  Q4K_CUDA(q4k::launch_gemv_tma_multi(ws, outs, count, swiglu, view(q8), plan, base + kTicketRegion, reinterpret_cast<uint32_t*>(base),
+                                      status, stream),
+           "decode_mmv.fused");
+  *fused = true;
+  return Q4K_OK;
+}
+
 int decode_pack(const q4k_decode_desc& d, const DecodeScratch& s, int* failure, cudaStream_t stream) {
   if (d.activation_policy == Q4K_ACTIVATION_BF16) return Q4K_OK;  // that policy multiplies the bf16 input as it is
   if (!failure) return fail(Q4K_ERR_INVALID_ARGUMENT, "decode_mmv: null failure flag");
@@ -603,6 +701,9 @@ int q4k_decode_mmv(const q4k_decode_desc* desc, void* workspace, uint64_t worksp
   DecodeScratch s{};
   if (int st = carve_decode_scratch(workspace, workspace_bytes, desc->m, desc->weight.n, desc->weight.k, &s)) return st;
   if (int st = decode_pack(*desc, s, failure, stream)) return st;
+  bool fused = false;
+  if (int st = decode_fused(&desc, 1, false, s.q8, stream, &fused)) return st;
+  if (fused) return Q4K_OK;
   return decode_one(*desc, s.q8, s.rows, stream);
 }
 
@@ -628,6 +729,12 @@ int q4k_decode_mmv_paired(const q4k_decode_desc* a, const q4k_decode_desc* b, vo
   if (int st = carve_decode_scratch(workspace, workspace_bytes, a->m, a->weight.n, a->weight.k, &s)) return st;
   if (int st = decode_pack(*a, s, failure, stream)) return st;
   uint64_t const cells = uint64_t(a->m) * a->weight.n;
+  {
+    const q4k_decode_desc* pair[2] = {a, &bv};
+    bool fused = false;
+    if (int st = decode_fused(pair, 2, swiglu, s.q8, stream, &fused)) return st;
+    if (fused) return Q4K_OK;
+  }
   if (!swiglu) {
     if (int st = decode_one(*a, s.q8, s.rows, stream)) return st;
     return decode_one(*b, s.q8, s.rows + cells, stream);
@@ -692,10 +799,57 @@ int q4k_decode_mmv_ranges(const q4k_decode_desc* ranges, uint32_t count, void* w
   DecodeScratch s{};
   if (int st = carve_decode_scratch(workspace, workspace_bytes, ranges[0].m, n_total, ranges[0].weight.k, &s)) return st;
   if (int st = decode_pack(ranges[0], s, failure, stream)) return st;
+  {
+    const q4k_decode_desc* list[3] = {&ranges[0], &ranges[1], count > 2 ? &ranges[2] : nullptr};
+    bool fused = false;
+    if (int st = decode_fused(list, count, false, s.q8, stream, &fused)) return st;
+    if (fused) return Q4K_OK;
+  }
   uint64_t off = 0;
   for (uint32_t i = 0; i < count; ++i) {
     if (int st = decode_one(ranges[i], s.q8, s.rows + off, stream)) return st;
     off += uint64_t(ranges[i].m) * ranges[i].weight.n;
+  }
+  return Q4K_OK;
+}
+
+struct q4k_session {
+  int device;
+  void* workspace;
+  uint64_t workspace_bytes;
+  int* failure;
+};
+
+int q4k_session_create(uint64_t workspace_bytes, q4k_session** out) {
+  if (!out || workspace_bytes == 0) return fail(Q4K_ERR_INVALID_ARGUMENT, "session: workspace_bytes and out must be given");
+  *out = nullptr;
+  int device = 0;
+  Q4K_CUDA(cudaGetDevice(&device), "cudaGetDevice");
+  uint64_t const bytes = (workspace_bytes + 255) / 256 * 256;
+  void* p = nullptr;
+  Q4K_CUDA(cudaMalloc(&p, bytes + 256), "session.alloc");
+  cudaError_t st = cudaMemset(static_cast<uint8_t*>(p) + bytes, 0, 256);
+  if (st != cudaSuccess) { (void)cudaFree(p); return fail_cuda(st, "session.clear"); }
+  *out = new q4k_session{device, p, bytes, reinterpret_cast<int*>(static_cast<uint8_t*>(p) + bytes)};
+  return Q4K_OK;
+}
+void q4k_session_destroy(q4k_session* s) {
+  if (!s) return;
+  (void)cudaFree(s->workspace);
+  delete s;
+}
+void* q4k_session_workspace(const q4k_session* s) { return s ? s->workspace : nullptr; }
+uint64_t q4k_session_workspace_bytes(const q4k_session* s) { return s ? s->workspace_bytes : 0; }
+int* q4k_session_failure(const q4k_session* s) { return s ? s->failure : nullptr; }
+int q4k_session_take_failure(q4k_session* s, void* stream_handle) {
+  if (!s) return fail(Q4K_ERR_INVALID_ARGUMENT, "session: null");
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_handle);
+  int bad = 0;
+  Q4K_CUDA(cudaMemcpyAsync(&bad, s->failure, 4, cudaMemcpyDeviceToHost, stream), "session.failure");
+  Q4K_CUDA(cudaStreamSynchronize(stream), "session.sync");
+  if (bad) {
+    Q4K_CUDA(cudaMemsetAsync(s->failure, 0, 4, stream), "session.clear_failure");
+    return fail(Q4K_ERR_INVALID_ARGUMENT, "q8.producer: nonfinite producer or invalid Q8 scale");
   }
   return Q4K_OK;
 }
@@ -928,13 +1082,20 @@ int q4k_q8_mlp(const q4k_weight* gate, const q4k_weight* up, const q4k_weight* d
   q4k_q8_input xf{codes, scales, sums, uint64_t(m) * ffn, uint64_t(m) * (ffn / 32), uint64_t(m) * (ffn / 32), m, ffn, ffn};
   q4k_project_options opt{};
   opt.flags = kFlagTrustedSpans;  // every span was validated above
-  cudaError_t ce = q4k::launch_hidden_rms_q8(residual, gamma, eps, hidden, out_view(xh), failure, stream);
+  cudaError_t ce;
+  {
+    ScopedRange range("qw38:op name=hidden_rms_q8_pack m=%u n=%u k=%u", unsigned(m), unsigned(hidden), 1u);
+    ce = q4k::launch_hidden_rms_q8(residual, gamma, eps, hidden, out_view(xh), failure, stream);
+  }
   if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.rms_pack"));
-  if (int st = project_impl(gate, xh, g, uint64_t(m) * ffn, nullptr, 0, &opt, stream)) return bail(st);
-  if (int st = project_impl(up, xh, u, uint64_t(m) * ffn, nullptr, 0, &opt, stream)) return bail(st);
-  ce = q4k::launch_swiglu_pack_q8(g, u, out_view(xf), failure, stream);
+  if (int st = project_impl(gate, xh, g, uint64_t(m) * ffn, nullptr, 0, &opt, stream, false, "gate")) return bail(st);
+  if (int st = project_impl(up, xh, u, uint64_t(m) * ffn, nullptr, 0, &opt, stream, false, "up")) return bail(st);
+  {
+    ScopedRange range("qw38:op name=swiglu_q8_pack m=%u n=%u k=%u", unsigned(m), unsigned(ffn), 1u);
+    ce = q4k::launch_swiglu_pack_q8(g, u, out_view(xf), failure, stream);
+  }
   if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.swiglu_pack"));
-  if (int st = project_impl(down, xf, output, uint64_t(m) * hidden, residual, uint64_t(m) * hidden, &opt, stream))
+  if (int st = project_impl(down, xf, output, uint64_t(m) * hidden, residual, uint64_t(m) * hidden, &opt, stream, false, "down"))
     return bail(st);
   if (pending_failure) return Q4K_OK;
   int bad = 0;

@@ -49,6 +49,15 @@ constexpr int kProducer = 0, kFirstReducer = 1;  // then NT reducer warps, then 
 constexpr int kTabRow = 112, kTabMn = 64, kTabDd = 96, kTabBytes = 16 * kTabRow;
 constexpr int kMaxStages = 8;
 
+// One weight of a multi-weight launch: its destination (fp32, or bf16 rounded to nearest even), its optional residual
+// ([m][n] like the destination), its rows, its 16-row tiles and its first row in the concatenated split-K scratch.
+struct GtSegment {
+  float* out;
+  uint16_t* out_bf16;
+  const float* residual;
+  uint32_t n, tiles, row_base;
+};
+
 struct GtParams {
   const int8_t* xcodes;
   const float* xscales;
@@ -69,6 +78,10 @@ struct GtParams {
   uint32_t cw;               // consumer warps = super-blocks per K slice
   uint32_t split_k, tiles_per_range, stages;
   uint32_t red_slots;        // 1 or 2 hand-off buffers between the consumers and the reducer
+  // General form (one launch over up to three weights that share x, each with its own epilogue; or a gate / up pair
+  // whose 16-row tiles alternate and whose result is bf16(SiLU(gate) * up)).  nseg == 0: the plain form above.
+  GtSegment seg[3];
+  uint32_t nseg, pair, n_total;  // n_total: rows of all segments = row stride of the split-K scratch
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -100,10 +113,28 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) { return __
 __device__ __forceinline__ float2 mul2(float2 a, float2 b) { return __fmul2_rn(a, b); }
 __device__ __forceinline__ float2 as_f2(uint32_t x, uint32_t y) { return make_float2(__uint_as_float(x), __uint_as_float(y)); }
 
+// sigmoid / SiLU as the reference's decode epilogue states them (cuda/decode_mmv.cu:78-89): the exponential is
+// always taken of a non-positive number.
+__device__ __forceinline__ float silu_fp32(float u) {
+  float const e = expf(u >= 0.0f ? -u : u);
+  return u * (u >= 0.0f ? 1.0f / (1.0f + e) : e / (1.0f + e));
+}
+// Which weight a global tile index of a multi-weight launch belongs to, and the tile's index inside it.
+__device__ __forceinline__ void locate_tile(const GtParams& p, uint32_t T, uint32_t& s, uint32_t& local) {
+  if (p.pair) { s = T & 1u; local = T >> 1; return; }
+  s = 0; local = T;
+  if (p.nseg > 1 && local >= p.seg[0].tiles) {
+    local -= p.seg[0].tiles; s = 1;
+    if (p.nseg > 2 && local >= p.seg[1].tiles) { local -= p.seg[1].tiles; s = 2; }
+  }
+}
+
 // NT = token octets (1: m <= 8, 2: m <= 16).  MAXW bounds the block size for register allocation.
 template <int NT, int MAXW, bool Dump>
 __global__ void __launch_bounds__(MAXW * 32, 1)
-gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_constant__ CUtensorMap tm_meta, const GtParams p) {
+gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_constant__ CUtensorMap tm_meta,
+                const __grid_constant__ CUtensorMap tm_codes1, const __grid_constant__ CUtensorMap tm_meta1,
+                const __grid_constant__ CUtensorMap tm_codes2, const __grid_constant__ CUtensorMap tm_meta2, const GtParams p) {
   extern __shared__ uint8_t smem_raw[];
   uint32_t const smem = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint32_t const cw = p.cw, stages = p.stages;
@@ -155,9 +186,18 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       for (uint32_t it = 0; it < ntiles; ++it) {
         if (it >= stages && !mbar_wait(b_empty + 8 * s, ph, abort_flag, p.status, 0x510)) break;
         mbar_expect_tx(b_full + 8 * s, code_stage + meta_stage);
-        int const rg = int((t0 + it) * 2);
-        tma_3d(s_codes + s * code_stage, &tm_codes, 0, int(sb0 * 8), rg, b_full + 8 * s);
-        tma_3d(s_meta + s * meta_stage, &tm_meta, 0, int(sb0), rg, b_full + 8 * s);
+        const CUtensorMap* mc = &tm_codes;
+        const CUtensorMap* mm = &tm_meta;
+        uint32_t local = t0 + it;
+        if (p.nseg > 1) {
+          uint32_t sg;
+          locate_tile(p, t0 + it, sg, local);
+          if (sg == 1) { mc = &tm_codes1; mm = &tm_meta1; }
+          if (sg == 2) { mc = &tm_codes2; mm = &tm_meta2; }
+        }
+        int const rg = int(local * 2);
+        tma_3d(s_codes + s * code_stage, mc, 0, int(sb0 * 8), rg, b_full + 8 * s);
+        tma_3d(s_meta + s * meta_stage, mm, 0, int(sb0), rg, b_full + 8 * s);
         if (++s == stages) { s = 0; ph ^= 1; }
       }
     }
@@ -178,6 +218,68 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     bool const live0 = tok0 < p.m, live1 = tok0 + 1 < p.m;
     size_t const o0 = to_slices ? size_t(tok0) * p.n : size_t(tok0) * p.out_stride + p.out_row0;
     size_t const o1 = o0 + (to_slices ? p.n : p.out_stride);
+    if (p.nseg != 0) {
+      // General form: every tile belongs to one of up to three weights with its own destination and epilogue; in
+      // pair mode the even tiles are the gate's, the odd ones the up projection's, and bf16(SiLU(gate) * up) is
+      // written once both are known.  Same hand-off and summation order as the plain form below.
+      float g00 = 0.f, g01 = 0.f, g10 = 0.f, g11 = 0.f;
+      for (uint32_t it = 0; it < ntiles; ++it) {
+        uint32_t const s = it & slot_mask, use = it >> slot_shift;
+        if (!mbar_wait(b_rfull + 8 * s, use & 1, abort_flag, p.status, 0x520)) break;
+        float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);
+        uint32_t src = s_red + s * red_slot + nt * 512 + lane * 16;
+#pragma unroll 4
+        for (uint32_t w = 0; w < nact; ++w) {
+          float4 const v = lds128f(src);
+          lo = __fadd2_rn(lo, make_float2(v.x, v.y));
+          hi = __fadd2_rn(hi, make_float2(v.z, v.w));
+          src += NT * 512;
+        }
+        mbar_arrive(b_rempty + 8 * s);
+        uint32_t sg, local;
+        locate_tile(p, t0 + it, sg, local);
+        const GtSegment& S = p.seg[sg];
+        uint32_t const row = local * 16 + r;
+        bool const in0 = row < S.n, in1 = row + 8 < S.n;
+        float v00 = lo.x, v01 = lo.y, v10 = hi.x, v11 = hi.y;
+        if (to_slices) {  // K slice: plain partial sums, rows of all weights side by side
+          float* const d0 = p.slices + (size_t(slice) * p.m + tok0) * p.n_total + S.row_base + row;
+          float* const d1 = d0 + p.n_total;
+          if (in0 && live0) d0[0] = v00;
+          if (in0 && live1) d1[0] = v01;
+          if (in1 && live0) d0[8] = v10;
+          if (in1 && live1) d1[8] = v11;
+          continue;
+        }
+        size_t const a0 = size_t(tok0) * S.n + row, a1 = a0 + S.n;
+        if (p.pair) {
+          if (sg == 0) { g00 = v00; g01 = v01; g10 = v10; g11 = v11; continue; }
+          uint16_t* const ob = p.seg[0].out_bf16;
+          if (in0 && live0) ob[a0] = f32_to_bf16_rne(silu_fp32(g00) * v00);
+          if (in0 && live1) ob[a1] = f32_to_bf16_rne(silu_fp32(g01) * v01);
+          if (in1 && live0) ob[a0 + 8] = f32_to_bf16_rne(silu_fp32(g10) * v10);
+          if (in1 && live1) ob[a1 + 8] = f32_to_bf16_rne(silu_fp32(g11) * v11);
+          continue;
+        }
+        if (S.residual) {
+          if (in0 && live0) v00 += S.residual[a0];
+          if (in0 && live1) v01 += S.residual[a1];
+          if (in1 && live0) v10 += S.residual[a0 + 8];
+          if (in1 && live1) v11 += S.residual[a1 + 8];
+        }
+        if (S.out_bf16) {
+          if (in0 && live0) S.out_bf16[a0] = f32_to_bf16_rne(v00);
+          if (in0 && live1) S.out_bf16[a1] = f32_to_bf16_rne(v01);
+          if (in1 && live0) S.out_bf16[a0 + 8] = f32_to_bf16_rne(v10);
+          if (in1 && live1) S.out_bf16[a1 + 8] = f32_to_bf16_rne(v11);
+        } else {
+          if (in0 && live0) S.out[a0] = v00;
+          if (in0 && live1) S.out[a1] = v01;
+          if (in1 && live0) S.out[a0 + 8] = v10;
+          if (in1 && live1) S.out[a1 + 8] = v11;
+        }
+      }
+    } else
     for (uint32_t it = 0; it < ntiles; ++it) {
       uint32_t const s = it & slot_mask, use = it >> slot_shift;
       if (!mbar_wait(b_rfull + 8 * s, use & 1, abort_flag, p.status, 0x520)) break;
@@ -396,6 +498,34 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       if (old == p.split_k - 1) p.tickets[range] = 0;
     }
     __syncthreads();
+    if (*last_flag && p.nseg != 0) {
+      __threadfence();
+      // One thread per (token, row of a tile); in pair mode per row of a gate tile, which also reads the up tile.
+      uint32_t const step = p.pair ? 2u : 1u;
+      size_t const plane = size_t(p.m) * p.n_total;
+      for (uint32_t i = threadIdx.x; i < (ntiles / step) * 16 * p.m; i += blockDim.x) {
+        uint32_t const tile = i / (16 * p.m), rem = i % (16 * p.m), tok = rem / 16, r16 = rem % 16;
+        uint32_t sg, local;
+        locate_tile(p, t0 + tile * step, sg, local);
+        const GtSegment& S = p.seg[sg];
+        uint32_t const row = local * 16 + r16;
+        if (row >= S.n) continue;
+        size_t const o = size_t(tok) * p.n_total + S.row_base + row;
+        float v = __ldcg(p.slices + o);
+        for (uint32_t sl = 1; sl < p.split_k; ++sl) v += __ldcg(p.slices + sl * plane + o);
+        size_t const oo = size_t(tok) * S.n + row;
+        if (p.pair) {
+          size_t const o2 = size_t(tok) * p.n_total + p.seg[1].row_base + row;
+          float u = __ldcg(p.slices + o2);
+          for (uint32_t sl = 1; sl < p.split_k; ++sl) u += __ldcg(p.slices + sl * plane + o2);
+          p.seg[0].out_bf16[oo] = f32_to_bf16_rne(silu_fp32(v) * u);
+          continue;
+        }
+        if (S.residual) v += S.residual[oo];
+        if (S.out_bf16) S.out_bf16[oo] = f32_to_bf16_rne(v);
+        else S.out[oo] = v;
+      }
+    } else
     if (*last_flag) {
       __threadfence();
       uint32_t const row0 = t0 * 16, rows = min(p.n, t1 * 16) > row0 ? min(p.n, t1 * 16) - row0 : 0;
@@ -442,13 +572,37 @@ uint32_t smem_bytes(uint32_t cw, uint32_t nt, uint32_t stages, uint32_t red_slot
   return 1024 + stages * cw * 2304 + cw * (kTabBytes + nt * 256) + red_slots * cw * nt * 512 + (2 * stages + 4) * 8 + 16;
 }
 
+struct Maps {
+  CUtensorMap codes[3], meta[3];
+};
+
 template <int NT, int MAXW>
-cudaError_t launch_cfg(const CUtensorMap& tm_codes, const CUtensorMap& tm_meta, const GtParams& p, bool dump, uint32_t grid,
-                       uint32_t smem, cudaStream_t stream) {
+cudaError_t launch_cfg(const Maps& t, const GtParams& p, bool dump, uint32_t grid, uint32_t smem, cudaStream_t stream) {
   auto kernel = dump ? gemv_tma_kernel<NT, MAXW, true> : gemv_tma_kernel<NT, MAXW, false>;
   cudaError_t st = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
   if (st != cudaSuccess) return st;
-  return launch_kernel(kernel, grid, (p.cw + kFirstReducer + NT) * 32, smem, stream, launch_overlap(), tm_codes, tm_meta, p);
+  return launch_kernel(kernel, grid, (p.cw + kFirstReducer + NT) * 32, smem, stream, launch_overlap(), t.codes[0], t.meta[0],
+                       t.codes[1], t.meta[1], t.codes[2], t.meta[2], p);
+}
+
+bool make_weight_maps(const WeightView& w, uint32_t cw, CUtensorMap* codes, CUtensorMap* meta) {
+  uint64_t const rgs = w.padded_n / 8;
+  uint64_t dims[3] = {128, uint64_t(w.tiles_k) * 8, rgs}, strides[2] = {128, uint64_t(w.tiles_k) * 1024};
+  uint32_t box[3] = {128, cw * 8, 2};
+  if (!make_map(codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B)) return false;
+  uint64_t mdims[3] = {128, w.tiles_k, rgs}, mstrides[2] = {128, uint64_t(w.tiles_k) * 128};
+  uint32_t mbox[3] = {128, cw, 2};
+  return make_map(meta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.meta, mdims, mstrides, mbox, CU_TENSOR_MAP_SWIZZLE_NONE);
+}
+
+template <class... A>
+cudaError_t launch_by_shape(uint32_t nt, uint32_t cw, A&&... a) {
+  if (nt == 1) {
+    if (cw <= 12) return launch_cfg<1, 14>(a...);
+    return launch_cfg<1, kGemvTmaMaxWarpsNarrow + 2>(a...);
+  }
+  if (cw <= 12) return launch_cfg<2, 15>(a...);
+  return launch_cfg<2, kGemvTmaMaxWarpsWide + 3>(a...);
 }
 
 }  // namespace
@@ -459,10 +613,14 @@ bool gemv_tma_supported(const WeightView& w, const Q8View& x) {
 }
 
 GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request, uint32_t warps_request) {
+  return plan_gemv_tma_tiles(m, ((n + 7) / 8 * 8 + 15) / 16, tiles_k, split_k_request, warps_request, false);
+}
+
+GemvTmaPlan plan_gemv_tma_tiles(uint32_t m, uint32_t row_tiles, uint32_t tiles_k, uint32_t split_k_request, uint32_t warps_request,
+                                bool pair) {
   GemvTmaPlan p;
   uint32_t const nt = m <= 8 ? 1 : 2;
   uint32_t const max_cw = nt == 1 ? kGemvTmaMaxWarpsNarrow : kGemvTmaMaxWarpsWide;
-  uint32_t const row_tiles = ((n + 7) / 8 * 8 + 15) / 16;
   uint32_t split = split_k_request;
   if (split == 0) {
     // Widest K slice by default.  Sixteen tokens on a matrix with few row tiles per SM measured faster
@@ -483,6 +641,7 @@ GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t spl
   if (ranges < 1) ranges = 1;
   if (ranges > row_tiles) ranges = row_tiles;
   p.tiles_per_range = (row_tiles + ranges - 1) / ranges;
+  if (pair && (p.tiles_per_range & 1u)) ++p.tiles_per_range;  // a gate tile and its up tile stay in one block
   p.ranges = (row_tiles + p.tiles_per_range - 1) / p.tiles_per_range;
   // Two hand-off buffers unless giving one up buys a third (or second) ring stage.
   auto fit = [&](uint32_t slots) {
@@ -507,20 +666,10 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
       (plan.split_k > 1 && (!slices || !tickets)) ||
       (gather && (gather->ranks < 1 || gather->ranks > 8 || gather->rank >= gather->ranks || !gather->done || !gather->unsignalled || partials)))
     return cudaErrorInvalidValue;
-  CUtensorMap tm_codes, tm_meta;
-  uint64_t const rgs = w.padded_n / 8;
-  {
-    uint64_t dims[3] = {128, uint64_t(w.tiles_k) * 8, rgs}, strides[2] = {128, uint64_t(w.tiles_k) * 1024};
-    uint32_t box[3] = {128, cw * 8, 2};
-    if (!make_map(&tm_codes, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.codes, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B))
-      return cudaErrorInvalidValue;
-  }
-  {
-    uint64_t dims[3] = {128, w.tiles_k, rgs}, strides[2] = {128, uint64_t(w.tiles_k) * 128};
-    uint32_t box[3] = {128, cw, 2};
-    if (!make_map(&tm_meta, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, w.meta, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_NONE))
-      return cudaErrorInvalidValue;
-  }
+  Maps t{};
+  if (!make_weight_maps(w, cw, &t.codes[0], &t.meta[0])) return cudaErrorInvalidValue;
+  t.codes[1] = t.codes[2] = t.codes[0];
+  t.meta[1] = t.meta[2] = t.meta[0];
   GtParams p{};
   p.xcodes = x.codes; p.xscales = x.scales; p.xsums = x.sums; p.residual = residual;
   if (gather) {
@@ -536,12 +685,39 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
   p.tiles_per_range = plan.tiles_per_range; p.stages = plan.stages; p.red_slots = plan.red_slots;
   uint32_t const grid = plan.ranges * plan.split_k, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
   bool const dump = partials != nullptr;
-  if (nt == 1) {
-    if (cw <= 12) return launch_cfg<1, 14>(tm_codes, tm_meta, p, dump, grid, smem, stream);
-    return launch_cfg<1, kGemvTmaMaxWarpsNarrow + 2>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+  return launch_by_shape(nt, cw, t, p, dump, grid, smem, stream);
+}
+
+cudaError_t launch_gemv_tma_multi(const WeightView* ws, const GemvTmaOutput* outs, uint32_t count, bool swiglu_pair, const Q8View& x,
+                                  const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream) {
+  uint32_t const nt = x.m <= 8 ? 1 : 2;
+  uint32_t const cw = plan.warps;
+  if (count < 1 || count > 3 || (swiglu_pair && count != 2) || x.m == 0 || x.m > kGemvTmaMaxTokens || cw < 1 ||
+      cw > (nt == 1 ? kGemvTmaMaxWarpsNarrow : kGemvTmaMaxWarpsWide) || plan.stages < 2 || plan.stages > uint32_t(kMaxStages) ||
+      (plan.red_slots != 1 && plan.red_slots != 2) || smem_bytes(cw, nt, plan.stages, plan.red_slots) > kSmemBudget ||
+      (plan.split_k > 1 && (!slices || !tickets)) || (swiglu_pair && (plan.tiles_per_range & 1u)))
+    return cudaErrorInvalidValue;
+  Maps t{};
+  GtParams p{};
+  uint32_t total_tiles = 0, total_rows = 0;
+  for (uint32_t i = 0; i < count; ++i) {
+    if (ws[i].tiles_k != ws[0].tiles_k || plan.split_k * cw < ws[i].tiles_k) return cudaErrorInvalidValue;
+    if (swiglu_pair && (ws[i].n != ws[0].n || !outs[0].out_bf16)) return cudaErrorInvalidValue;
+    if (!swiglu_pair && !outs[i].out && !outs[i].out_bf16) return cudaErrorInvalidValue;
+    if (!make_weight_maps(ws[i], cw, &t.codes[i], &t.meta[i])) return cudaErrorInvalidValue;
+    p.seg[i] = GtSegment{outs[i].out, outs[i].out_bf16, outs[i].residual, ws[i].n, (ws[i].padded_n + 15) / 16, total_rows};
+    total_tiles += p.seg[i].tiles;
+    total_rows += ws[i].n;
   }
-  if (cw <= 12) return launch_cfg<2, 15>(tm_codes, tm_meta, p, dump, grid, smem, stream);
-  return launch_cfg<2, kGemvTmaMaxWarpsWide + 3>(tm_codes, tm_meta, p, dump, grid, smem, stream);
+  for (uint32_t i = count; i < 3; ++i) { t.codes[i] = t.codes[0]; t.meta[i] = t.meta[0]; }
+  p.xcodes = x.codes; p.xscales = x.scales; p.xsums = x.sums;
+  p.ndst = 1; p.slices = static_cast<float*>(slices); p.tickets = tickets; p.status = status;
+  p.n = ws[0].n; p.m = x.m; p.padded_k = x.padded_k; p.tiles_k = ws[0].tiles_k; p.G = x.padded_k / 32;
+  p.row_tiles = total_tiles; p.cw = cw; p.split_k = plan.split_k;
+  p.tiles_per_range = plan.tiles_per_range; p.stages = plan.stages; p.red_slots = plan.red_slots;
+  p.nseg = count; p.pair = swiglu_pair ? 1u : 0u; p.n_total = total_rows;
+  uint32_t const grid = plan.ranges * plan.split_k, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
+  return launch_by_shape(nt, cw, t, p, false, grid, smem, stream);
 }
 
 }  // namespace q4k

@@ -112,6 +112,20 @@ struct GemvTmaGather {
   uint32_t* unsignalled;  // finished-but-unannounced projections of this rank (shared with peer wait)
   uint32_t ranks, rank, row_offset, total_rows;
 };
+GemvTmaPlan plan_gemv_tma_tiles(uint32_t m, uint32_t row_tiles, uint32_t tiles_k, uint32_t split_k_request, uint32_t warps_request,
+                                bool pair);
+// One launch over up to three weights that share x (and K), each with its own destination and epilogue: fp32 or bf16
+// (round to nearest even) store, optional fp32 residual of the destination's shape added last.  swiglu_pair: exactly
+// two weights of equal shape, gate and up; their 16-row tiles alternate through the blocks and the single result
+// bf16(SiLU(gate) * up) goes to outs[0].out_bf16.  Plan from plan_gemv_tma_tiles over the tiles of all weights
+// (16-row tiles of each padded_n; split-K scratch rows = sum of n).
+struct GemvTmaOutput {
+  float* out;
+  uint16_t* out_bf16;
+  const float* residual;
+};
+cudaError_t launch_gemv_tma_multi(const WeightView* ws, const GemvTmaOutput* outs, uint32_t count, bool swiglu_pair, const Q8View& x,
+                                  const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream);
 cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
                             const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream,
                             const GemvTmaGather* gather = nullptr);

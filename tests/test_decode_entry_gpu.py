@@ -71,9 +71,11 @@ def test_decode_mmv_epilogues(m):
     assert (canary == 7.0).all()
 
 
-@pytest.mark.parametrize("m", [1, 8])
-def test_decode_mmv_paired_swiglu_and_ranges(m):
-    n, k = 1000, 2048
+@pytest.mark.parametrize("m,n,k", [(1, 1000, 2048), (8, 1000, 2048), (16, 640, 17408), (3, 136, 17408), (9, 34816 // 8, 5120)])
+def test_decode_mmv_paired_swiglu_and_ranges(m, n, k):
+    """One launch per call: the gate / up pair's tiles alternate through the blocks and the reducer writes
+    bf16(SiLU(gate) * up); ranges and plain pairs walk their weights' tiles one after the other.  K = 17408 runs with
+    K slices through the global scratch (the epilogue is then applied by the last block of a row range)."""
     wa, x, ref_a = setup(n, k, m, seed=11)
     codes, meta = synth.logical_q4k(n, k, seed=12)
     hc, hs = synth.split_tiles(codes, meta)

@@ -41,3 +41,22 @@ def test_shim_runs_the_path_on_the_device(tmp_path):
     assert r.returncode == 0, r.stdout + r.stderr
     r = subprocess.run([str(exe)], capture_output=True, text=True)
     assert r.returncode == 0 and "shim gpu check ok" in r.stdout, r.stdout + r.stderr
+
+
+@pytest.mark.gpu
+def test_reference_operator_case_through_the_shim(tmp_path):
+    """The reference's own test case for this path (tests/q4k_q8_test.cpp:36-142), restated in C++ against the shim:
+    ten token counts, one PASS line each."""
+    gxx = shutil.which("g++")
+    cuda = Path("/usr/local/cuda")
+    if gxx is None or not (cuda / "include" / "cuda_runtime.h").exists():
+        pytest.skip("no g++ or CUDA headers")
+    lib = build.build()
+    exe = tmp_path / "q4k_q8_case"
+    cmd = [gxx, "-std=c++23", "-O1", "-Wall", "-Wextra", f"-I{ROOT / 'include'}", f"-I{cuda / 'include'}",
+           str(ROOT / "tests" / "shim" / "q4k_q8_case.cpp"), "-o", str(exe), f"-L{lib.parent}", "-lq4k_b200",
+           f"-L{cuda / 'lib64'}", "-lcudart", f"-Wl,-rpath,{lib.parent}", f"-Wl,-rpath,{cuda / 'lib64'}"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0 and r.stdout.count(" PASS") == 10, r.stdout + r.stderr
