@@ -47,6 +47,8 @@
 // Every wait on an mbarrier is bounded: after ~2 s a thread raises the block's abort flag and
 // the kernel's status word, all roles leave their loops, TMEM is freed and the kernel returns.
 #include <cuda.h>
+#include <stdlib.h>
+
 
 #include "common.cuh"
 #include "launch.h"
@@ -60,7 +62,13 @@ constexpr int kRows = 128;
 constexpr int kProducerWarp = 0, kMmaWarp = 1, kFirstExpander = 2;
 constexpr uint32_t kPreset = 1u << 17;  // what the constant MMA leaves in every accumulator: 32 * 64 * 64
 constexpr uint32_t kConstByte = 0x40404040u;
-constexpr int kConstBytes = 16 * 1024;  // 128 rows of 128 bytes, the layout of the data operands (every byte equal, so the swizzle is moot)
+// The int32 word 2^17 + P of an accumulator, read as fp32 bits, is (2^17 + P) * 2^-149.  The token-side table holds
+// a' = a * 2^89 and c' = -a' * 2^-132 (so that fma(word, a', c') = a * P * 2^-60 with one rounding), the row-side
+// table S = d * sc * 2^60.  Scales above 2^38 would overflow a': their super-block takes the slower loop.
+constexpr float kTokScalePow = 0x1p89f, kRowScalePow = 0x1p60f, kBiasOut = -0x1p-132f, kWideAbove = 0x1p38f;
+// The constant operand: every byte equal, so neither the swizzle nor which bytes a row reads matters, and the 8-row
+// atoms may overlap: the descriptor gives them a stride of 128 bytes instead of 1024 (16 atoms end at 15 * 128 + 1024).
+constexpr int kConstBytes = 4 * 1024, kConstAtomStride = 128;
 
 // NTOK tokens per tile; NCOL <= NTOK accumulator columns actually drained (8 when m <= 8).
 //
@@ -145,12 +153,24 @@ struct TcParams {
   uint32_t* tickets;
   int* status;
   uint32_t n, m, tiles_k, split_k, G, row_tiles, tok_tiles;
+#ifdef Q4K_TC_TRACE
+  long long* trace;
+#endif
 };
+#ifdef Q4K_TC_TRACE
+#define TRACE_AT(cond, idx) do { if (p.trace && blockIdx.x == 0 && lane == 0 && (cond)) p.trace[idx] = clock64(); } while (0)
+#else
+#define TRACE_AT(cond, idx) do { } while (0)
+#endif
 
 // Accumulator patch of 16 TMEM lanes x (8 * NB) columns in the MMA C-fragment layout: register
 // 4j + 2i + e of lane l = (lane 8i + l / 4, column 8j + 2 (l % 4) + e) of the patch.
 template <int NB> __device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, uint32_t* r) {
   static_assert(NB == 1 || NB == 2 || NB == 4, "column blocks per load");
+#ifdef Q4K_UP_ONLY
+  for (int i = 0; i < 4 * NB; ++i) r[i] = 0;
+  return;
+#endif
   if constexpr (NB == 1) {
     asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr));
@@ -173,6 +193,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], uint32_t a0, uint32_t a1
       "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// The same with a zero accumulator input (no registers to clear first).
+__device__ __forceinline__ void mma_bf16_first(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+      : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
 }
 __device__ __forceinline__ float2 lds64f(uint32_t a) {
   float2 v;
@@ -269,6 +296,11 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     }
   };
 
+#ifdef Q4K_EPI_ONLY
+  uint32_t const up_tiles = 0;
+#else
+  uint32_t const up_tiles = num_tiles;
+#endif
   if (warp < C::kFirstEpilogue) {
   if constexpr (C::kRebalance) {
     static_assert(C::kFirstEpilogue % 4 == 0 && C::kWarps == 24, "register split assumes 8 + 16 warps");
@@ -279,7 +311,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
         uint32_t row_tile, tok_tile, slice, kb0, kb1;
         tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
         int const rg0 = int(row_tile * (kRows / 8));
@@ -299,7 +331,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       // int8 tiles straight into the operand ring.
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
         uint32_t row_tile, tok_tile, slice, kb0, kb1;
         tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
         int const tok0 = int(tok_tile * NTOK);
@@ -318,10 +350,10 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8(NTOK);
-      uint64_t const cdesc = umma_desc_sw128(smem_u32(smem + C::oConst));
+      uint64_t const cdesc = umma_desc_sw128(smem_u32(smem + C::oConst), kConstAtomStride);
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+      for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
         uint32_t row_tile, tok_tile, slice, kb0, kb1;
         tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
         for (uint32_t kb = kb0; ok && kb < kb1; ++kb, ++it) {
@@ -356,7 +388,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     constexpr uint32_t kEntries = (NTOK * 8 + kET - 1) / kET;  // activation-table entries per thread
     uint32_t it = 0;
     bool ok = true;
-    for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+    for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
       uint32_t row_tile, tok_tile, slice, kb0, kb1;
       tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
       uint32_t const tok0 = tok_tile * NTOK;
@@ -408,7 +440,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         // as bf16, one 16-byte row each (the A operand of the min-term MMA).
         for (uint32_t row = et; row < kRows; row += kET) {
           uint4 const cm = lds128(raw + C::oRawMeta + row * 16);
-          float const d100 = fp16_bits_to_f32(cm.x & 0xffffu) * 0x1p100f, ndmin = -fp16_bits_to_f32(cm.x >> 16);
+          float const dS = fp16_bits_to_f32(cm.x & 0xffffu) * kRowScalePow, ndmin = -fp16_bits_to_f32(cm.x >> 16);
           ScaleMinWords const sm = decode_scale_min(cm.y, cm.z, cm.w);
           uint32_t const slot = (row >> 5) * 32 + (row & 7) * 4 + ((row >> 3) & 3);
           uint32_t const st = scl + C::oS + slot * 4;
@@ -416,7 +448,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
             uint32_t const scw = g < 4 ? sm.sc_lo : sm.sc_hi, mnw = g < 4 ? sm.mn_lo : sm.mn_hi;
-            sts32f(st + g * kRows * 4, d100 * float(byte_of(scw, g & 3)));
+            sts32f(st + g * (kRows * 4), dS * float(byte_of(scw, g & 3)));
             uint32_t const mbits = __float_as_uint(float(byte_of(mnw, g & 3))) >> 16;  // a six-bit integer is exact in bf16
             if (g & 1) mb[g >> 1] |= mbits << 16; else mb[g >> 1] = mbits;
           }
@@ -430,7 +462,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         for (uint32_t e = 0; e < kEntries; ++e) {
           uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
           if (j < NTOK * 8) {
-            sts32f(scl + C::oAf + (g * NTOK + tk) * 4, av[e] * 0x1p49f);
+            sts32f(scl + C::oAf + (g * NTOK + tk) * 4, av[e] * kTokScalePow);
             float const as = av[e] * float(sv[e]);
             uint16_t const t0 = f32_to_bf16_rne(as);
             float const r1 = as - bf16_bits_to_f32(t0);
@@ -440,7 +472,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             sts16(dst, t0);
             sts16(dst + 16, t1);
             sts16(dst + 32, t2);
-            if (av[e] > 0x1p78f) atomicMax(reinterpret_cast<uint32_t*>(smem + C::oSclRing + sc * C::kSclStage + C::oWide), it + 1);
+            if (av[e] > kWideAbove) atomicMax(reinterpret_cast<uint32_t*>(smem + C::oSclRing + sc * C::kSclStage + C::oWide), it + 1);
           }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's async proxy
@@ -476,16 +508,19 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     // in flight while the current half is folded: tcgen05.ld has a latency of several hundred cycles, and four
     // epilogue warps per scheduler cannot hide it by themselves.
     uint32_t const lane_base = tmem_base + ((quarter * 32u) << 16) + col0;
-    uint32_t rA[4 * NB], rB[4 * NB];
+    constexpr int NBL = NB >= 2 ? NB / 2 : 1, CH = NB / NBL;  // column blocks per read, reads per half
+    uint32_t rA[4 * NBL], rB[4 * NBL];
     constexpr int PER = C::kMmaPerCommit / GS;  // groups of this warp per accumulator set
     auto fetch_first_half = [&](uint32_t it2, uint32_t g2, bool wait_set) -> bool {  // group g2 of super-block it2 into rA
       uint32_t b2, parity2;
       acc_slot<C::kAccBufs>(it2, g2, b2, parity2);
       if (wait_set) {
+#ifndef Q4K_EPI_ONLY
         if (!mbar_wait_inline<512, 128>(bar_acc_full(b2 / C::kMmaPerCommit), parity2, abort_flag, p.status, 10)) return false;
+#endif
         tc_fence_after();
       }
-      tmem_ld_frag<NB>(lane_base + b2 * NTOK, rA);
+      tmem_ld_frag<NBL>(lane_base + b2 * NTOK, rA);
       return true;
     };
     if (blockIdx.x < num_tiles) ok = fetch_first_half(0, gs, true);
@@ -502,117 +537,130 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       for (uint32_t kb = kb0; ok && kb < kb1; ++kb, ++it) {
         uint32_t const sc = it % C::kScl;
         bool const has_next = kb + 1 < kb1 || t + gridDim.x < num_tiles;
+#ifndef Q4K_EPI_ONLY
         if (!mbar_wait_inline<512, 128>(bar_s_full(sc), (it / C::kScl) & 1, abort_flag, p.status, 9)) { ok = false; break; }
+#endif
         uint32_t const scl = smem_s + C::oSclRing + sc * C::kSclStage;
         bool const wide = lds32(scl + C::oWide) == it + 1;
-        uint32_t const stab = scl + C::oS + (quarter * 8 + R0) * 16;
+        uint32_t const ssp = scl + C::oS + (quarter * 8 + R0) * 16;  // this lane's four row scales of group g: + g * 512
+        uint32_t const afp = scl + C::oAf + (col0 + 2 * q) * 4;      // a' of tokens col0 + 8j + 2q, +1 of group g: + g * NTOK * 4 + 32 j
         // ---- min term of the whole super-block on the tensor cores: rows x groups (six-bit mins, bf16) times
         // groups x tokens (a * sum in three bf16 terms; products exact, fp32 accumulation), scaled by -dmin.
         // (Where the groups are split over several warps, the first of them adds it.)
+#ifdef Q4K_UP_ONLY
+        if (false) {
+#else
         if (GS == 1 || gs == 0) {
+#endif
           uint32_t const mrow = scl + C::oMt + (quarter * 32 + R0) * 16 + q * 4;
           uint32_t const am00 = lds32(mrow), am01 = lds32(mrow + 8 * 16), am10 = lds32(mrow + 16 * 16), am11 = lds32(mrow + 24 * 16);
           float4 const nd4 = lds128f(scl + C::oNd + (quarter * 8 + R0) * 16);
-          float const nd[4] = {nd4.x, nd4.y, nd4.z, nd4.w};
+          float2 const nd2[4] = {make_float2(nd4.x, nd4.x), make_float2(nd4.y, nd4.y), make_float2(nd4.z, nd4.z), make_float2(nd4.w, nd4.w)};
 #pragma unroll
           for (int j = 0; j < NB; ++j) {
             uint32_t const brow = scl + C::oAsT + (col0 + 8 * j + R0) * 48 + q * 4;
             uint32_t const b0 = lds32(brow), b1 = lds32(brow + 16), b2 = lds32(brow + 32);
-            float m0[4] = {0.f, 0.f, 0.f, 0.f}, m1[4] = {0.f, 0.f, 0.f, 0.f};
-            mma_bf16(m0, am00, am01, am00, am01, b2, 0u);
-            mma_bf16(m1, am10, am11, am10, am11, b2, 0u);
+            float m0[4], m1[4];
+            mma_bf16_first(m0, am00, am01, am00, am01, b2, 0u);
+            mma_bf16_first(m1, am10, am11, am10, am11, b2, 0u);
             mma_bf16(m0, am00, am01, am00, am01, b0, b1);
             mma_bf16(m1, am10, am11, am10, am11, b0, b1);
 #pragma unroll
             for (int i2 = 0; i2 < 2; ++i2) {
-              acc[0][j][i2] = __ffma2_rn(make_float2(nd[i2], nd[i2]), make_float2(m0[2 * i2], m0[2 * i2 + 1]), acc[0][j][i2]);
-              acc[1][j][i2] = __ffma2_rn(make_float2(nd[2 + i2], nd[2 + i2]), make_float2(m1[2 * i2], m1[2 * i2 + 1]), acc[1][j][i2]);
+              acc[0][j][i2] = __ffma2_rn(nd2[i2], make_float2(m0[2 * i2], m0[2 * i2 + 1]), acc[0][j][i2]);
+              acc[1][j][i2] = __ffma2_rn(nd2[2 + i2], make_float2(m1[2 * i2], m1[2 * i2 + 1]), acc[1][j][i2]);
             }
           }
         }
-        // One trip per accumulator set (PER groups of this warp), unrolled inside: what depends on the position in
-        // the set is decided at compile time, and the code stays small enough not to spill.
-#pragma unroll 1
-        for (int ts = 0; ts < 8 / GS / PER; ++ts) {
-#pragma unroll
-        for (int tu = 0; tu < PER; ++tu) {
-          int const tt = ts * PER + tu;
+        // ---- one K32 group: tt-th group of this warp in the super-block.  With tt known at compile time (the
+        // unrolled fast path) every decision about sets and successors is static and each TMEM read has one site.
+        auto group = [&](bool const slow, int const tt) -> bool {
           uint32_t const g = gs + GS * tt;
-          bool const last_of_set = tu == PER - 1;
-          // S and c = -S * 2^-132 (= -D * 2^-32, exact) of this lane's four rows
-          float4 const S4 = lds128f(stab + g * (kRows * 4));
-          float2 const k2 = make_float2(-0x1p-132f, -0x1p-132f);
-          float2 const c01 = __fmul2_rn(make_float2(S4.x, S4.y), k2), c23 = __fmul2_rn(make_float2(S4.z, S4.w), k2);
-          float const Sr[4] = {S4.x, S4.y, S4.z, S4.w}, cr[4] = {c01.x, c01.y, c23.x, c23.y};
-          uint32_t const afp = scl + C::oAf + (g * NTOK + col0 + 2 * q) * 4;
-          float2 f[NB];  // a' of tokens col0 + 8j + 2q, + 1
+          bool const last_of_set = (tt % PER) == PER - 1;
+          uint32_t b, parity;
+          acc_slot<C::kAccBufs>(it, g, b, parity);
+          float4 const S4 = lds128f(ssp + g * (kRows * 4));
+          float2 A[NB], Cc[NB];
 #pragma unroll
-          for (int j = 0; j < NB; ++j) f[j] = lds64f(afp + 32 * j);
-          if (wide) {  // plain scales from global memory; the products below then carry the 2^49 themselves
+          for (int j = 0; j < NB; ++j) A[j] = lds64f(afp + g * (NTOK * 4) + 32 * j);
+          if (slow) {  // plain scales from global memory; the accumulator words are scaled by 2^89 first instead
 #pragma unroll
             for (int j = 0; j < NB; ++j) {
               uint32_t const tk = tok0 + 8 * j;
-              f[j].x = tk < p.m ? p.xscales[size_t(tk) * p.G + kb * 8 + g] : 0.f;
-              f[j].y = tk + 1 < p.m ? p.xscales[size_t(tk + 1) * p.G + kb * 8 + g] : 0.f;
+              A[j].x = tk < p.m ? p.xscales[size_t(tk) * p.G + kb * 8 + g] : 0.f;
+              A[j].y = tk + 1 < p.m ? p.xscales[size_t(tk + 1) * p.G + kb * 8 + g] : 0.f;
             }
           }
-          uint32_t b, parity;
-          acc_slot<C::kAccBufs>(it, g, b, parity);
-          auto fold = [&](const uint32_t (&r)[4 * NB], int h) {
-            if (!wide) {
+          float const kc = slow ? -0x1p-43f : kBiasOut;
 #pragma unroll
-              for (int j = 0; j < NB; ++j) {
+          for (int j = 0; j < NB; ++j) Cc[j] = __fmul2_rn(A[j], make_float2(kc, kc));
+          float const Sr[4] = {S4.x, S4.y, S4.z, S4.w};
+          // The 32 x CW patch is read in 2 * CH steps of 16 TMEM lanes x (8 * NBL) columns, alternately into rA and
+          // rB: the read of the next step (or of the next group's first) is in flight while a step is folded.
+          auto fold = [&](const uint32_t (&r)[4 * NBL], int h, int c) {
+#ifdef Q4K_UP_ONLY
+            return;
+#endif
 #pragma unroll
-                for (int i2 = 0; i2 < 2; ++i2) {
-                  int const k = 2 * h + i2;
-                  float2 const v = __ffma2_rn(as_f2(r[4 * j + 2 * i2], r[4 * j + 2 * i2 + 1]), make_float2(Sr[k], Sr[k]), make_float2(cr[k], cr[k]));  // D * P * 2^-49
-                  acc[h][j][i2] = __ffma2_rn(f[j], v, acc[h][j][i2]);                                                   // + a * (D * P)
-                }
-              }
-            } else {
+            for (int i2 = 0; i2 < 2; ++i2) {
+              float2 const s2 = make_float2(Sr[2 * h + i2], Sr[2 * h + i2]);
 #pragma unroll
-              for (int j = 0; j < NB; ++j) {
-#pragma unroll
-                for (int i2 = 0; i2 < 2; ++i2) {
-                  int const k = 2 * h + i2;
-                  float2 v = __ffma2_rn(as_f2(r[4 * j + 2 * i2], r[4 * j + 2 * i2 + 1]), make_float2(Sr[k], Sr[k]), make_float2(cr[k], cr[k]));
-                  v = __fmul2_rn(v, make_float2(0x1p49f, 0x1p49f));
-                  acc[h][j][i2] = __ffma2_rn(f[j], v, acc[h][j][i2]);
-                }
+              for (int jj = 0; jj < NBL; ++jj) {
+                int const j = c * NBL + jj;
+                float2 w = as_f2(r[4 * jj + 2 * i2], r[4 * jj + 2 * i2 + 1]);
+                if (slow) w = __fmul2_rn(w, make_float2(kTokScalePow, kTokScalePow));
+                float2 const v = __ffma2_rn(w, A[j], Cc[j]);          // a * P * 2^-60
+                acc[h][j][i2] = __ffma2_rn(s2, v, acc[h][j][i2]);  // + (D * 2^60) * that
               }
             }
             if (Dump) {
 #pragma unroll
-              for (int v = 0; v < 4 * NB; ++v) {
-                uint32_t const row = row0 + 16 * h + 8 * ((v >> 1) & 1), token = tok0 + 8 * (v >> 2) + (v & 1);
+              for (int v = 0; v < 4 * NBL; ++v) {
+                uint32_t const row = row0 + 16 * h + 8 * ((v >> 1) & 1), token = tok0 + 8 * (c * NBL + (v >> 2)) + (v & 1);
                 if (row < p.n && token < p.m)
                   p.partials[(uint64_t(token) * p.n + row) * p.G + kb * 8 + g] = int32_t(r[v] - kPreset);
               }
             }
           };
-          // first half: in rA; the second half of the same group goes out before it is folded
-          tmem_wait_ld();
-          tmem_ld_frag<NB>(lane_base + (16u << 16) + b * NTOK, rB);
-          fold(rA, 0);
-          // second half: in rB; with it the warp has read all it wants of this group
-          tmem_wait_ld();
-          if (last_of_set) {  // the set goes back to the MMA warp
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_acc_empty(b / C::kMmaPerCommit));
+          bool got = true;
+#pragma unroll
+          for (int st = 0; st < 2 * CH; ++st) {
+            int const h = st & 1, c = st >> 1;
+            tmem_wait_ld();  // step st has arrived
+            if (st + 1 < 2 * CH) {
+              int const h1 = (st + 1) & 1, c1 = (st + 1) >> 1;
+              if ((st & 1) == 0) tmem_ld_frag<NBL>(lane_base + (uint32_t(16 * h1) << 16) + b * NTOK + 8 * NBL * c1, rB);
+              else tmem_ld_frag<NBL>(lane_base + (uint32_t(16 * h1) << 16) + b * NTOK + 8 * NBL * c1, rA);
+            } else {
+              // with its last step the warp has read all it wants of this group
+              if (last_of_set) {  // the set goes back to the MMA warp
+                tc_fence_before();
+                __syncwarp();
+#ifndef Q4K_EPI_ONLY
+                if (lane == 0) mbar_arrive(bar_acc_empty(b / C::kMmaPerCommit));
+#endif
+              }
+              if (tt + 1 < 8 / GS) got = fetch_first_half(it, g + GS, last_of_set);
+              else if (has_next) got = fetch_first_half(it + 1, gs, true);
+            }
+            if ((st & 1) == 0) fold(rA, h, c); else fold(rB, h, c);
           }
-          if (tt + 1 < 8 / GS) {
-            if (!fetch_first_half(it, g + GS, last_of_set)) { ok = false; break; }
-          } else if (has_next) {
-            if (!fetch_first_half(it + 1, gs, true)) { ok = false; break; }
-          }
-          fold(rB, 1);
-        }
-        if (!ok) break;
+          return got;
+        };
+        if (!wide) {
+#pragma unroll
+          for (int tt = 0; tt < 8 / GS; ++tt)
+            if (ok && !group(false, tt)) ok = false;
+        } else {
+#pragma unroll 1
+          for (int tt = 0; tt < 8 / GS; ++tt)
+            if (ok && !group(true, tt)) ok = false;
         }
         if (!ok) break;
         __syncwarp();
+#ifndef Q4K_EPI_ONLY
         if (lane == 0) mbar_arrive(bar_s_free(sc));
+#endif
       }
       if (!ok) break;
 
@@ -764,6 +812,9 @@ cudaError_t launch_ntok(const WeightView& w, const Q8View& x, const TcOutput& o,
   p.out_bf16 = o.out_bf16; p.ndst = o.ndst; p.out_stride = o.stride ? o.stride : w.n; p.out_row0 = o.row0;
   p.partials = partials; p.partial_tiles = partial_tiles; p.tickets = tickets; p.status = status;
   p.n = w.n; p.m = x.m; p.tiles_k = w.tiles_k; p.split_k = split_k; p.G = uint32_t(G); p.row_tiles = row_tiles; p.tok_tiles = tok_tiles;
+#ifdef Q4K_TC_TRACE
+  if (const char* e = getenv("Q4K_TC_TRACE")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 16));
+#endif
   uint64_t const tiles = uint64_t(row_tiles) * tok_tiles * split_k;
   uint32_t const grid = uint32_t(tiles < uint64_t(sm_count()) ? tiles : uint64_t(sm_count()));
   kernel<<<grid, C::kThreads, C::kSmem, stream>>>(tm_codes, tm_meta, tm_act, p);

@@ -59,11 +59,16 @@ template <uint32_t MaxNs = 256, uint32_t FirstNs = 32>
 __device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try(bar, parity)) return true;
   long long const t0 = clock64();
-  uint32_t ns = FirstNs;
+#ifndef Q4K_WAIT_SCALE
+#define Q4K_WAIT_SCALE 1
+#endif
+  uint32_t ns = FirstNs * Q4K_WAIT_SCALE;
   for (uint32_t tries = 1;; ++tries) {
+#ifndef Q4K_WAIT_SPIN
     __nanosleep(ns);
+#endif
     if (mbar_try(bar, parity)) return true;
-    if (ns < MaxNs) ns *= 2;
+    if (ns < MaxNs * Q4K_WAIT_SCALE) ns *= 2;
     if ((tries & 7u) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitCycles) {
@@ -99,6 +104,7 @@ __device__ __forceinline__ void sts128f(uint32_t a, float x, float y, float z, f
   asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(a), "f"(x), "f"(y), "f"(z), "f"(w) : "memory");
 }
 __device__ __forceinline__ void sts32f(uint32_t a, float x) { asm volatile("st.shared.f32 [%0], %1;" ::"r"(a), "f"(x) : "memory"); }
+__device__ __forceinline__ void sts64f(uint32_t a, float x, float y) { asm volatile("st.shared.v2.f32 [%0], {%1,%2};" ::"r"(a), "f"(x), "f"(y) : "memory"); }
 
 __device__ __forceinline__ void tma_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"

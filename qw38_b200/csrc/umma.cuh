@@ -8,8 +8,8 @@ namespace q4k {
 // K-major operand in the 128-byte-swizzled layout: rows of 128 bytes, 8-row atoms of 1024 bytes
 // (stride between atoms 1024), 16-byte chunk index XORed with (row & 7).  Descriptor version 1
 // (sm_100), layout type 2.  A K32 slice of int8 data starts 32 bytes further along the row.
-__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
-  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(1024 >> 4) << 32) | (uint64_t(1) << 46) |
+__device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr, uint32_t atom_stride = 1024) {
+  return uint64_t((saddr & 0x3FFFFu) >> 4) | (uint64_t(1) << 16) | (uint64_t(atom_stride >> 4) << 32) | (uint64_t(1) << 46) |
          (uint64_t(2) << 61);
 }
 // K-major operand without swizzle: core matrices of 8 rows x 16 bytes (128 contiguous bytes);
