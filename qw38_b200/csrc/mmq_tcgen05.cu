@@ -82,19 +82,33 @@ constexpr int kConstBytes = 4 * 1024, kConstAtomStride = 128;
 //   S (scales)   per-row metadata copy and the activation-scale table; freed by the epilogue.
 // Epilogue warps: every warp may only touch the TMEM lanes of its quarter (warp % 4).
 template <int NTOK, int NCOL> struct Cfg {
-  static constexpr int kColSplit = NTOK >= 128 ? 4 : (NTOK >= 64 ? 2 : (NTOK >= 32 ? 2 : 1));
+  static constexpr int kColSplit = NTOK >= 128 ? 4 : (NTOK >= 32 ? 2 : 1);
   static constexpr int kGroupSplit = NTOK >= 64 ? 1 : 2;
   static constexpr int kEpilogueWarps = 4 * kColSplit * kGroupSplit;
   // Roles are aligned to groups of four warps (the register file is shared by the four warps that sit
   // on one scheduler each): producer + MMA + expanders fill the first groups, the epilogue the rest.
-  static constexpr int kExpanders = NTOK >= 64 ? 6 : 10;
+#ifndef Q4K_EXP64
+#define Q4K_EXP64 6
+#endif
+#ifndef Q4K_EXP128
+#define Q4K_EXP128 6
+#endif
+#ifndef Q4K_EXP32
+#define Q4K_EXP32 10
+#endif
+  static constexpr int kExpanders = NTOK >= 128 ? Q4K_EXP128 : (NTOK >= 64 ? Q4K_EXP64 : Q4K_EXP32);
   // Wide tiles: the non-epilogue warps give registers back, the epilogue warps take them
   // (setmaxnreg); 24 warps start at 80 registers each.
-  static constexpr bool kRebalance = NTOK >= 128;
-  static constexpr int kRegsLow = 48, kRegsHigh = 96;  // 8 * 48 + 16 * 96 = 24 * 80: the block's own allocation is the pool
+  static constexpr bool kRebalance = NTOK >= 128 || NTOK == 32;
+  // The block's own allocation is the pool: 24 warps start at 80 registers (8 * 48 + 16 * 96 = 24 * 80), 28 warps at 72
+  // (12 * 48 + 16 * 88 <= 28 * 72).
+  static constexpr int kRegsLow = 48;
   static constexpr int kFirstEpilogue = kFirstExpander + kExpanders;
   static constexpr int kWarps = kFirstEpilogue + kEpilogueWarps;
   static constexpr int kThreads = kWarps * 32;
+  static constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8 > 128 ? 128 : (65536 / kThreads) / 8 * 8;
+  static constexpr int kRegsHighRaw = (kWarps * kRegsLaunch - kFirstEpilogue * kRegsLow) / kEpilogueWarps / 8 * 8;
+  static constexpr int kRegsHigh = kRegsHighRaw > 112 ? 112 : kRegsHighRaw;
   static constexpr int kColsPerWarp = NCOL / kColSplit;
   static constexpr int kAccBufs = (512 / NTOK) > 16 ? 16 : (512 / NTOK);
   // One tcgen05.commit, one wait and one release per set of two (narrow tiles: four) K32 groups: barrier
@@ -102,9 +116,9 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kMmaPerCommit = NTOK <= 32 ? 4 : 2;
   static constexpr int kAccSets = kAccBufs / kMmaPerCommit;
   // ring depths
-  static constexpr int kRaw = NTOK <= 16 ? 4 : (NTOK <= 64 ? 3 : 2);
+  static constexpr int kRaw = NTOK <= 16 ? 5 : (NTOK <= 32 ? 4 : (NTOK <= 64 ? 5 : 3));
   static constexpr int kOps = 2;
-  static constexpr int kScl = NTOK >= 128 ? 2 : 3;
+  static constexpr int kScl = NTOK >= 64 ? 2 : 3;
   // raw stage
   static constexpr int kRawCodes = 16 * 1024, kRawMeta = 16 * 128;
   static constexpr int oRawCodes = 0, oRawMeta = kRawCodes;
@@ -119,7 +133,8 @@ template <int NTOK, int NCOL> struct Cfg {
   //              | six-bit mins as bf16 [row][8] | a' = a * 2^49 [group][token] | a * sum as three bf16 terms
   //              [token][term][group] | stamp of the last stage with an overflowing a'
   static constexpr int kRowTab = 8 * kRows * 4;
-  static constexpr int oS = 0, oNd = kRowTab, oMt = oNd + kRows * 4, oAf = oMt + kRows * 16, oAsT = oAf + 8 * NTOK * 4,
+  static constexpr int kAfStride = NTOK + 4;  // floats between groups of the a' table: the expanders' stores (eight groups x four tokens per warp) then fall into 32 different banks
+  static constexpr int oS = 0, oNd = kRowTab, oMt = oNd + kRows * 4, oAf = oMt + kRows * 16, oAsT = oAf + 8 * kAfStride * 4,
                        oWide = oAsT + NTOK * 48;
   static constexpr int kSclStage = (oWide + 16 + 127) / 128 * 128;
   // whole layout
@@ -303,7 +318,8 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
 #endif
   if (warp < C::kFirstEpilogue) {
   if constexpr (C::kRebalance) {
-    static_assert(C::kFirstEpilogue % 4 == 0 && C::kWarps == 24, "register split assumes 8 + 16 warps");
+    static_assert(C::kFirstEpilogue % 4 == 0 && C::kFirstEpilogue * C::kRegsLow + C::kEpilogueWarps * C::kRegsHigh <= C::kWarps * ((65536 / C::kThreads) / 8 * 8),
+                  "the register split must fit the block's allocation");
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsLow));
   }
   if (warp == kProducerWarp) {
@@ -363,20 +379,25 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
           tc_fence_after();
           uint8_t* const st = smem + C::oOps + o * C::kOpStage;
           uint32_t const a_base = smem_u32(st + C::oAExp), b_base = smem_u32(st + C::oB);
+          // Set by set: the constant MMAs of all its buffers first, then the data MMAs, so that an MMA that accumulates
+          // on a preset does not queue directly behind the MMA that writes it.
 #pragma unroll
-          for (uint32_t g = 0; g < 8; ++g) {
-            uint32_t b, parity;
-            acc_slot<C::kAccBufs>(it, g, b, parity);
-            uint32_t const set = b / C::kMmaPerCommit;
-            if (g % C::kMmaPerCommit == 0) {
-              if (!mbar_wait_inline<256, 64>(bar_acc_empty(set), parity ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
-              tc_fence_after();
+          for (uint32_t g0 = 0; g0 < 8; g0 += C::kMmaPerCommit) {
+            uint32_t b0, parity;
+            acc_slot<C::kAccBufs>(it, g0, b0, parity);
+            uint32_t const set = b0 / C::kMmaPerCommit;
+            if (!mbar_wait_inline<256, 64>(bar_acc_empty(set), parity ^ 1, abort_flag, p.status, 5)) { ok = false; break; }
+            tc_fence_after();
+#pragma unroll
+            for (uint32_t k = 0; k < C::kMmaPerCommit; ++k) umma_i8(tmem_base + (b0 + k) * NTOK, cdesc, cdesc, idesc, 0);  // every accumulator = 2^17
+#pragma unroll
+            for (uint32_t k = 0; k < C::kMmaPerCommit; ++k) {
+              uint32_t const g = g0 + k;
+              uint64_t const ad = umma_desc_sw128(a_base + (g >> 2) * (kRows * 128) + (g & 3) * 32);
+              uint64_t const bd = umma_desc_sw128(b_base + (g >> 2) * (NTOK * 128) + (g & 3) * 32);
+              umma_i8(tmem_base + (b0 + k) * NTOK, ad, bd, idesc, 1);  // += the K32 dots
             }
-            uint64_t const ad = umma_desc_sw128(a_base + (g >> 2) * (kRows * 128) + (g & 3) * 32);
-            uint64_t const bd = umma_desc_sw128(b_base + (g >> 2) * (NTOK * 128) + (g & 3) * 32);
-            umma_i8(tmem_base + b * NTOK, cdesc, cdesc, idesc, 0);  // every accumulator = 2^17
-            umma_i8(tmem_base + b * NTOK, ad, bd, idesc, 1);        // += the K32 dots
-            if (g % C::kMmaPerCommit == C::kMmaPerCommit - 1) umma_commit(bar_acc_full(set));
+            umma_commit(bar_acc_full(set));
           }
           if (ok) umma_commit(bar_op_free(o));  // operands are free once these MMAs have read them
         }
@@ -403,8 +424,12 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
           uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
           bool const live = j < NTOK * 8 && tok0 + tk < p.m;
           size_t const idx = size_t(tok0 + tk) * p.G + kb * 8 + g;
+#ifndef Q4K_SKIP_ACT
           av[e] = live ? __ldg(p.xscales + idx) : 0.f;
           sv[e] = live ? __ldg(p.xsums + idx) : 0;
+#else
+          av[e] = 0.f; sv[e] = int(live);
+#endif
         }
         if (!mbar_wait_inline<1024, 128>(bar_raw_full(r), (it / C::kRaw) & 1, abort_flag, p.status, 6)) { ok = false; break; }
         if (!mbar_wait_inline<1024, 128>(bar_op_free(o), ((it / C::kOps) & 1) ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
@@ -415,6 +440,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         // 1024 raw 16-byte chunks = (row of the tile, K32 group).  A quarter warp takes the eight rows of one
         // 8-row atom, lane i the row i and the group (g0 + i) mod 8: its eight reads and each of its two sets of
         // eight writes fall into eight different 16-byte bank groups.
+#ifndef Q4K_SKIP_EXPAND
         {
           uint32_t const i8 = et & 7;
 #pragma unroll 2
@@ -435,9 +461,11 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             sts128(dst + (((c + 1) ^ i8) << 4), ov[4], ov[5], ov[6], ov[7]);
           }
         }
+#endif
         // Row tables: S = d * sc * 2^100 of every (row, group) and -dmin of every row, laid out so that an epilogue
         // lane finds its four rows (l/4, +8, +16, +24 of its lane quarter) in one 16-byte word; the six-bit mins
         // as bf16, one 16-byte row each (the A operand of the min-term MMA).
+#ifndef Q4K_SKIP_ROWTAB
         for (uint32_t row = et; row < kRows; row += kET) {
           uint4 const cm = lds128(raw + C::oRawMeta + row * 16);
           float const dS = fp16_bits_to_f32(cm.x & 0xffffu) * kRowScalePow, ndmin = -fp16_bits_to_f32(cm.x >> 16);
@@ -455,14 +483,16 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
           sts128(scl + C::oMt + row * 16, mb[0], mb[1], mb[2], mb[3]);
           sts32f(scl + C::oNd + slot * 4, ndmin);
         }
+#endif
         // Activation tables: a' = a * 2^49 per (group, token), and a * sum split into three bf16 terms that add up to
         // it exactly (the B operand of the min-term MMA).  A scale so large that a' is not finite stamps the stage,
         // and the epilogue then works from the plain scales.
+#ifndef Q4K_SKIP_ACT
 #pragma unroll
         for (uint32_t e = 0; e < kEntries; ++e) {
           uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
           if (j < NTOK * 8) {
-            sts32f(scl + C::oAf + (g * NTOK + tk) * 4, av[e] * kTokScalePow);
+            sts32f(scl + C::oAf + (g * C::kAfStride + tk) * 4, av[e] * kTokScalePow);
             float const as = av[e] * float(sv[e]);
             uint16_t const t0 = f32_to_bf16_rne(as);
             float const r1 = as - bf16_bits_to_f32(t0);
@@ -475,6 +505,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             if (av[e] > kWideAbove) atomicMax(reinterpret_cast<uint32_t*>(smem + C::oSclRing + sc * C::kSclStage + C::oWide), it + 1);
           }
         }
+#endif
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's async proxy
         __syncwarp();
         if (lane == 0) {
@@ -508,10 +539,15 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     // in flight while the current half is folded: tcgen05.ld has a latency of several hundred cycles, and four
     // epilogue warps per scheduler cannot hide it by themselves.
     uint32_t const lane_base = tmem_base + ((quarter * 32u) << 16) + col0;
-    constexpr int NBL = NB >= 2 ? NB / 2 : 1, CH = NB / NBL;  // column blocks per read, reads per half
-    uint32_t rA[4 * NBL], rB[4 * NBL];
+    // A unit = this warp's 32 rows x (8 * UB) tokens of one K32 group, read as two 16-lane halves.  The reads of the
+    // next unit -- of the same group, of the warp's next group, or of the next super-block's first -- are in flight
+    // while a unit is folded (two buffers, used alternately): tcgen05.ld has a latency of a hundred cycles and
+    // more under load, tcgen05.wait::ld waits for everything outstanding, and a unit's arithmetic is short.
+    constexpr int UB = NB >= 2 ? 2 : 1, U = NB / UB;  // column blocks per unit, units per group
+    uint32_t bufA[2][4 * UB], bufB[2][4 * UB];
     constexpr int PER = C::kMmaPerCommit / GS;  // groups of this warp per accumulator set
-    auto fetch_first_half = [&](uint32_t it2, uint32_t g2, bool wait_set) -> bool {  // group g2 of super-block it2 into rA
+    // Issues the reads of unit u of group g2 of super-block it2; first waits for the group's accumulator set when asked.
+    auto fetch_unit = [&](uint32_t (&dst)[2][4 * UB], uint32_t it2, uint32_t g2, int u, bool wait_set) -> bool {
       uint32_t b2, parity2;
       acc_slot<C::kAccBufs>(it2, g2, b2, parity2);
       if (wait_set) {
@@ -520,10 +556,12 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
 #endif
         tc_fence_after();
       }
-      tmem_ld_frag<NBL>(lane_base + b2 * NTOK, rA);
+      uint32_t const ta = lane_base + b2 * NTOK + 8 * UB * u;
+      tmem_ld_frag<UB>(ta, dst[0]);
+      tmem_ld_frag<UB>(ta + (16u << 16), dst[1]);
       return true;
     };
-    if (blockIdx.x < num_tiles) ok = fetch_first_half(0, gs, true);
+    if (blockIdx.x < num_tiles) ok = fetch_unit(bufA, 0, gs, 0, true);
     for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
       uint32_t row_tile, tok_tile, slice, kb0, kb1;
       tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
@@ -537,6 +575,8 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       for (uint32_t kb = kb0; ok && kb < kb1; ++kb, ++it) {
         uint32_t const sc = it % C::kScl;
         bool const has_next = kb + 1 < kb1 || t + gridDim.x < num_tiles;
+        bool const tr_on = ep == 0 && it >= 6 && it < 8;
+        TRACE_AT(tr_on, 96 + (it - 6) * 3);
 #ifndef Q4K_EPI_ONLY
         if (!mbar_wait_inline<512, 128>(bar_s_full(sc), (it / C::kScl) & 1, abort_flag, p.status, 9)) { ok = false; break; }
 #endif
@@ -572,6 +612,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             }
           }
         }
+        TRACE_AT(tr_on, 96 + (it - 6) * 3 + 2);
         // ---- one K32 group: tt-th group of this warp in the super-block.  With tt known at compile time (the
         // unrolled fast path) every decision about sets and successors is static and each TMEM read has one site.
         auto group = [&](bool const slow, int const tt) -> bool {
@@ -580,59 +621,29 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
           uint32_t b, parity;
           acc_slot<C::kAccBufs>(it, g, b, parity);
           float4 const S4 = lds128f(ssp + g * (kRows * 4));
-          float2 A[NB], Cc[NB];
-#pragma unroll
-          for (int j = 0; j < NB; ++j) A[j] = lds64f(afp + g * (NTOK * 4) + 32 * j);
-          if (slow) {  // plain scales from global memory; the accumulator words are scaled by 2^89 first instead
-#pragma unroll
-            for (int j = 0; j < NB; ++j) {
-              uint32_t const tk = tok0 + 8 * j;
-              A[j].x = tk < p.m ? p.xscales[size_t(tk) * p.G + kb * 8 + g] : 0.f;
-              A[j].y = tk + 1 < p.m ? p.xscales[size_t(tk + 1) * p.G + kb * 8 + g] : 0.f;
-            }
-          }
-          float const kc = slow ? -0x1p-43f : kBiasOut;
-#pragma unroll
-          for (int j = 0; j < NB; ++j) Cc[j] = __fmul2_rn(A[j], make_float2(kc, kc));
           float const Sr[4] = {S4.x, S4.y, S4.z, S4.w};
-          // The 32 x CW patch is read in 2 * CH steps of 16 TMEM lanes x (8 * NBL) columns, alternately into rA and
-          // rB: the read of the next step (or of the next group's first) is in flight while a step is folded.
-          auto fold = [&](const uint32_t (&r)[4 * NBL], int h, int c) {
-#ifdef Q4K_UP_ONLY
-            return;
-#endif
-#pragma unroll
-            for (int i2 = 0; i2 < 2; ++i2) {
-              float2 const s2 = make_float2(Sr[2 * h + i2], Sr[2 * h + i2]);
-#pragma unroll
-              for (int jj = 0; jj < NBL; ++jj) {
-                int const j = c * NBL + jj;
-                float2 w = as_f2(r[4 * jj + 2 * i2], r[4 * jj + 2 * i2 + 1]);
-                if (slow) w = __fmul2_rn(w, make_float2(kTokScalePow, kTokScalePow));
-                float2 const v = __ffma2_rn(w, A[j], Cc[j]);          // a * P * 2^-60
-                acc[h][j][i2] = __ffma2_rn(s2, v, acc[h][j][i2]);  // + (D * 2^60) * that
-              }
-            }
-            if (Dump) {
-#pragma unroll
-              for (int v = 0; v < 4 * NBL; ++v) {
-                uint32_t const row = row0 + 16 * h + 8 * ((v >> 1) & 1), token = tok0 + 8 * (c * NBL + (v >> 2)) + (v & 1);
-                if (row < p.n && token < p.m)
-                  p.partials[(uint64_t(token) * p.n + row) * p.G + kb * 8 + g] = int32_t(r[v] - kPreset);
-              }
-            }
-          };
+          float const kc = slow ? -0x1p-43f : kBiasOut;
           bool got = true;
+          auto unit = [&](uint32_t (&cur)[2][4 * UB], uint32_t (&nxt)[2][4 * UB], int const u) {
+            // The token-side operands first: their shared-memory latency passes under the wait for TMEM.
+            float2 A[UB], Cc[UB];  // a' and c' of tokens col0 + 8j + 2q, +1 of this unit's column blocks j
 #pragma unroll
-          for (int st = 0; st < 2 * CH; ++st) {
-            int const h = st & 1, c = st >> 1;
-            tmem_wait_ld();  // step st has arrived
-            if (st + 1 < 2 * CH) {
-              int const h1 = (st + 1) & 1, c1 = (st + 1) >> 1;
-              if ((st & 1) == 0) tmem_ld_frag<NBL>(lane_base + (uint32_t(16 * h1) << 16) + b * NTOK + 8 * NBL * c1, rB);
-              else tmem_ld_frag<NBL>(lane_base + (uint32_t(16 * h1) << 16) + b * NTOK + 8 * NBL * c1, rA);
-            } else {
-              // with its last step the warp has read all it wants of this group
+            for (int jj = 0; jj < UB; ++jj) A[jj] = lds64f(afp + g * (C::kAfStride * 4) + 32 * (u * UB + jj));
+            if (slow) {  // plain scales from global memory; the accumulator words are scaled by 2^89 first instead
+#pragma unroll
+              for (int jj = 0; jj < UB; ++jj) {
+                uint32_t const tk = tok0 + 8 * (u * UB + jj);
+                A[jj].x = tk < p.m ? p.xscales[size_t(tk) * p.G + kb * 8 + g] : 0.f;
+                A[jj].y = tk + 1 < p.m ? p.xscales[size_t(tk + 1) * p.G + kb * 8 + g] : 0.f;
+              }
+            }
+#pragma unroll
+            for (int jj = 0; jj < UB; ++jj) Cc[jj] = __fmul2_rn(A[jj], make_float2(kc, kc));
+            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 0);
+            tmem_wait_ld();  // this unit has arrived
+            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 1);
+            if (u == U - 1) {
+              // with its last unit the warp has read all it wants of this group
               if (last_of_set) {  // the set goes back to the MMA warp
                 tc_fence_before();
                 __syncwarp();
@@ -640,10 +651,49 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
                 if (lane == 0) mbar_arrive(bar_acc_empty(b / C::kMmaPerCommit));
 #endif
               }
-              if (tt + 1 < 8 / GS) got = fetch_first_half(it, g + GS, last_of_set);
-              else if (has_next) got = fetch_first_half(it + 1, gs, true);
+              if (tt + 1 < 8 / GS) got = fetch_unit(nxt, it, g + GS, 0, last_of_set);
+              else if (has_next) got = fetch_unit(nxt, it + 1, gs, 0, true);
+            } else {
+              fetch_unit(nxt, it, g, u + 1, false);
             }
-            if ((st & 1) == 0) fold(rA, h, c); else fold(rB, h, c);
+            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 2);
+#ifndef Q4K_UP_ONLY
+            // All first FMAs (a * P * 2^-60), then all second ones (+ (D * 2^60) * that): no FMA waits for its predecessor.
+            float2 v[2][2][UB];
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int i2 = 0; i2 < 2; ++i2)
+#pragma unroll
+                for (int jj = 0; jj < UB; ++jj) {
+                  float2 w = as_f2(cur[h][4 * jj + 2 * i2], cur[h][4 * jj + 2 * i2 + 1]);
+                  if (slow) w = __fmul2_rn(w, make_float2(kTokScalePow, kTokScalePow));
+                  v[h][i2][jj] = __ffma2_rn(w, A[jj], Cc[jj]);
+                }
+#pragma unroll
+            for (int h = 0; h < 2; ++h)
+#pragma unroll
+              for (int i2 = 0; i2 < 2; ++i2) {
+                float2 const s2 = make_float2(Sr[2 * h + i2], Sr[2 * h + i2]);
+#pragma unroll
+                for (int jj = 0; jj < UB; ++jj) acc[h][u * UB + jj][i2] = __ffma2_rn(s2, v[h][i2][jj], acc[h][u * UB + jj][i2]);
+              }
+#endif
+            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 3);
+            if (Dump) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+#pragma unroll
+                for (int v = 0; v < 4 * UB; ++v) {
+                  uint32_t const row = row0 + 16 * h + 8 * ((v >> 1) & 1), token = tok0 + 8 * (u * UB + (v >> 2)) + (v & 1);
+                  if (row < p.n && token < p.m)
+                    p.partials[(uint64_t(token) * p.n + row) * p.G + kb * 8 + g] = int32_t(cur[h][v] - kPreset);
+                }
+            }
+          };
+#pragma unroll
+          for (int u = 0; u < U; ++u) {
+            if (((tt * U + u) & 1) == 0) unit(bufA, bufB, u); else unit(bufB, bufA, u);
           }
           return got;
         };

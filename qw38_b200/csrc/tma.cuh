@@ -64,7 +64,7 @@ __device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, 
 #endif
   uint32_t ns = FirstNs * Q4K_WAIT_SCALE;
   for (uint32_t tries = 1;; ++tries) {
-#ifndef Q4K_WAIT_SPIN
+#ifdef Q4K_WAIT_SLEEP
     __nanosleep(ns);
 #endif
     if (mbar_try(bar, parity)) return true;
