@@ -4,51 +4,60 @@
 // The per-K32 rule of the reference (cuda/q4k_q8.cu:70-72: one exact int32 dot per 32 columns,
 // never carried into the next group) fixes the structure: every data MMA has K = 32 and its
 // 128 x NTOK int32 results are drained from TMEM and folded into fp32 accumulators in registers
-// as  acc += a * (D * float(P)) - Mn * (a * float(sum)).
+// as  acc += D * (a * float(P)) - Mn * (a * float(sum)).
 //
-// Two resources bound such a kernel, and the design is built around both:
-//   * The fp32 pipe: three FMAs per partial is the floor of the equation, so nothing else may
-//     run there.  No int -> float conversion: before the data MMA of a group a second MMA of two
-//     constant tiles (every byte 64) writes 32 * 64 * 64 = 2^17 into every accumulator, and the
-//     data MMA accumulates on top.  The int32 word 2^17 + P, read as an fp32 bit pattern, is the
-//     (sub)normal number (2^17 + P) * 2^-149, an affine function of P, so one FMA with the row's
-//     scale S = D * 2^100 and the exact constant c = -D * 2^-32 yields D * P * 2^-49 with a single
-//     rounding.  The activation scale carries the inverse power of two, a' = a * 2^49, so the
-//     second FMA acc += a' * v is the reference's a * (D * P) to the bit.  Should a' overflow
-//     (|x| beyond ~5e27) the super-block takes a slower loop that reads the plain scale.
-//   * The shared-memory pipe: one wavefront per clock per SM.  An epilogue in which a thread owns
-//     one weight row and 32 tokens reads 32 activation scales per group as broadcasts, 4 bytes
-//     per wavefront, and saturates that pipe at a fifth of the fp32 floor.  So the accumulators
-//     are read in the 16x256b shape (the MMA C-fragment layout): a thread owns 4 rows x 8
-//     tokens of its warp's 32 x 32 patch, needs the scales of 8 tokens and 4 rows only, and a
-//     warp's loads are 64-byte segments instead of broadcasts.  The row scales come from a table
-//     the expander warps build once per super-block; the expanders themselves read and write
-//     without bank conflicts (lane i of a quarter warp takes row i of an 8-row atom and K32 group
-//     (g0 + i) mod 8).
+// What the design is built around (clock64 units on a B200, one block per SM):
+//   * Two packed FMAs per pair of partials and nothing else on the fp32 pipe.  No int -> float
+//     conversion: before the data MMA of a group a second MMA of two constant tiles (every byte
+//     64) writes 32 * 64 * 64 = 2^17 into every accumulator, and the data MMA accumulates on top.
+//     The int32 word 2^17 + P, read as an fp32 bit pattern, is the subnormal (2^17 + P) * 2^-149,
+//     an affine function of P, so one FMA with the token's scale a' = a * 2^89 and the exact
+//     constant c' = -a' * 2^-132 yields a * P * 2^-60 with a single rounding, and the second FMA
+//     acc += S * v with the row's S = d * sc * 2^60 completes the term.  The token side goes
+//     first because its operands are natural register pairs (two neighbouring tokens), whereas
+//     the row scale has to be duplicated into a pair.  Should a' overflow (scales beyond 2^38)
+//     the super-block takes a slower loop that reads the plain scale from global memory.
+//   * The min term  -dmin * sum_g m[n,g] * (a * sum)[t,g]  is a rank-8 update per super-block
+//     and runs on the warp-level tensor MMAs (mma.sync bf16): six-bit mins are exact in bf16,
+//     a * sum is split into three bf16 terms that add up to it exactly.
+//   * Shared memory (one 128-byte wavefront per clock) is shared by the MMA's operand fetch, the
+//     expanders and the epilogue's scale loads.  The accumulators are therefore read in the
+//     16x256b shape (the MMA C-fragment layout): a thread owns 4 rows x 8 tokens of its warp's
+//     32 x 32 patch and needs the scales of 8 tokens and 4 rows only (an owner of one row x 32
+//     tokens would read 32 token scales per group as broadcasts and saturate the pipe).  Tables
+//     are laid out so that expander stores and epilogue loads are free of bank conflicts.
+//   * tcgen05.ld in that shape delivers 256 B/clk per SM and has a latency of 65 clk unloaded,
+//     130 with sixteen warps reading; tcgen05.wait::ld waits for everything outstanding.  The
+//     epilogue therefore works in units of two reads (32 rows x 16 tokens) with the next unit's
+//     reads in flight, loads its scale operands under the TMEM wait and issues all first FMAs
+//     of a unit before the second ones.  The eight groups of a super-block are unrolled, so that
+//     every decision about accumulator sets and successors is static and each read has one site.
+//   * Every barrier hand-off costs several hundred clocks of exposed latency: accumulator
+//     buffers travel in sets (one commit, one wait, one release per set), waits spin on
+//     mbarrier.try_wait without back-off, and one thread polls both TMA streams.
 //
 // Tile: 128 weight rows (the M side, one TMEM lane per row) x NTOK tokens (the N side) per
 // block, K walked in 256-column super-blocks.  Warp roles:
-//   warp 0      lane 0 issues the raw TMA stream: 4-bit code tiles + metadata (3-D maps over the
-//               split tile layout, no swizzle); lane 1 issues the int8 activation tiles (2-D map,
-//               128-byte swizzle, rows beyond m zero-filled) into the operand ring;
-//   warp 1      allocates TMEM; one lane issues, per K32 group, the constant MMA and the data MMA
-//               into the next accumulator buffer, then tcgen05.commit;
-//   expanders   (6 to 10 warps) expand nibbles to int8 in the K-major 128-byte-swizzled operand
-//               layout, decode the six-bit scales into the row tables (S, -Mn) and build the
-//               (a', a'', a*sum, a*sum') table of the token pairs from the activations' scales and
-//               sums in global memory;
-//   epilogue    per K32 group tcgen05.ld its accumulator patch and scale.  Tiles of 64 / 128
-//               tokens: 16 warps, four column quarters per TMEM lane quarter; narrower tiles
-//               split the eight K32 groups over two warps per lane quarter (and 32-token tiles
-//               the columns in two) and add their sums in warp order at the end of a tile.
+//   warp 0      one lane issues both TMA streams: raw 4-bit code tiles + metadata (3-D maps over
+//               the split tile layout, no swizzle) into the raw ring, int8 activation tiles (2-D
+//               map, 128-byte swizzle, rows beyond m zero-filled) into the operand ring;
+//   warp 1      allocates TMEM; one lane issues, set by set, the constant MMAs and the data MMAs
+//               into the set's accumulator buffers, then tcgen05.commit;
+//   expanders   (6 or 10 warps) expand nibbles to int8 in the K-major 128-byte-swizzled operand
+//               layout, decode the six-bit scales into the row tables (S, -dmin, mins as bf16)
+//               and build the token tables (a', a * sum in three bf16 terms) from the
+//               activations' scales and sums in global memory;
+//   epilogue    tiles of 128 tokens: 16 warps, four column quarters per TMEM lane quarter; 64
+//               tokens: 8 warps, two column halves; narrower tiles split the eight K32 groups
+//               over two warps per lane quarter and add their sums in warp order at the end of
+//               a tile.  On the wide tiles the other warps hand registers to the epilogue warps
+//               (setmaxnreg).
 // The kernel is persistent (one block per SM walks the tile list), so TMEM allocation, barrier
 // set-up and pipeline fill are paid once and the loads of the next tile overlap the epilogue of
 // the current one.
 // Every wait on an mbarrier is bounded: after ~2 s a thread raises the block's abort flag and
 // the kernel's status word, all roles leave their loops, TMEM is freed and the kernel returns.
 #include <cuda.h>
-#include <stdlib.h>
-
 
 #include "common.cuh"
 #include "launch.h"
@@ -87,21 +96,11 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kEpilogueWarps = 4 * kColSplit * kGroupSplit;
   // Roles are aligned to groups of four warps (the register file is shared by the four warps that sit
   // on one scheduler each): producer + MMA + expanders fill the first groups, the epilogue the rest.
-#ifndef Q4K_EXP64
-#define Q4K_EXP64 6
-#endif
-#ifndef Q4K_EXP128
-#define Q4K_EXP128 6
-#endif
-#ifndef Q4K_EXP32
-#define Q4K_EXP32 10
-#endif
-  static constexpr int kExpanders = NTOK >= 128 ? Q4K_EXP128 : (NTOK >= 64 ? Q4K_EXP64 : Q4K_EXP32);
-  // Wide tiles: the non-epilogue warps give registers back, the epilogue warps take them
-  // (setmaxnreg); 24 warps start at 80 registers each.
+  static constexpr int kExpanders = NTOK >= 64 ? 6 : 10;  // measured: more expander warps on the wide tiles slow the block down
+  // Wide tiles: the non-epilogue warps give registers back, the epilogue warps take them (setmaxnreg).
   static constexpr bool kRebalance = NTOK >= 128 || NTOK == 32;
   // The block's own allocation is the pool: 24 warps start at 80 registers (8 * 48 + 16 * 96 = 24 * 80), 28 warps at 72
-  // (12 * 48 + 16 * 88 <= 28 * 72).
+  // (12 * 48 + 16 * 88 <= 28 * 72).  Asking for more than the pool holds blocks the warps forever.
   static constexpr int kRegsLow = 48;
   static constexpr int kFirstEpilogue = kFirstExpander + kExpanders;
   static constexpr int kWarps = kFirstEpilogue + kEpilogueWarps;
@@ -111,9 +110,9 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kRegsHigh = kRegsHighRaw > 112 ? 112 : kRegsHighRaw;
   static constexpr int kColsPerWarp = NCOL / kColSplit;
   static constexpr int kAccBufs = (512 / NTOK) > 16 ? 16 : (512 / NTOK);
-  // One tcgen05.commit, one wait and one release per set of two (narrow tiles: four) K32 groups: barrier
-  // traffic is pure overhead next to the arithmetic of a group.
-  static constexpr int kMmaPerCommit = NTOK <= 32 ? 4 : 2;
+  // One tcgen05.commit, one wait and one release per set of K32 groups (two on 128-token tiles, which have four
+  // buffers; four elsewhere): measured, one buffer per set costs 20-30 % and four per set beat two.
+  static constexpr int kMmaPerCommit = NTOK <= 64 ? 4 : 2;
   static constexpr int kAccSets = kAccBufs / kMmaPerCommit;
   // ring depths
   static constexpr int kRaw = NTOK <= 16 ? 5 : (NTOK <= 32 ? 4 : (NTOK <= 64 ? 5 : 3));
@@ -129,8 +128,8 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int oAExp = 0, oB = kAExp;
   static constexpr int kOpStage = (kAExp + kB + 1023) / 1024 * 1024;
   static constexpr int kBTx = kB;
-  // scale stage: row scales S = d * sc * 2^100 ([group][lane quarter][row & 7][row / 8 & 3]) | -dmin (same row order)
-  //              | six-bit mins as bf16 [row][8] | a' = a * 2^49 [group][token] | a * sum as three bf16 terms
+  // scale stage: row scales S = d * sc * 2^60 ([group][lane quarter][row & 7][row / 8 & 3]) | -dmin (same row order)
+  //              | six-bit mins as bf16 [row][8] | a' = a * 2^89 [group][token, padded] | a * sum as three bf16 terms
   //              [token][term][group] | stamp of the last stage with an overflowing a'
   static constexpr int kRowTab = 8 * kRows * 4;
   static constexpr int kAfStride = NTOK + 4;  // floats between groups of the a' table: the expanders' stores (eight groups x four tokens per warp) then fall into 32 different banks
@@ -168,24 +167,12 @@ struct TcParams {
   uint32_t* tickets;
   int* status;
   uint32_t n, m, tiles_k, split_k, G, row_tiles, tok_tiles;
-#ifdef Q4K_TC_TRACE
-  long long* trace;
-#endif
 };
-#ifdef Q4K_TC_TRACE
-#define TRACE_AT(cond, idx) do { if (p.trace && blockIdx.x == 0 && lane == 0 && (cond)) p.trace[idx] = clock64(); } while (0)
-#else
-#define TRACE_AT(cond, idx) do { } while (0)
-#endif
 
 // Accumulator patch of 16 TMEM lanes x (8 * NB) columns in the MMA C-fragment layout: register
 // 4j + 2i + e of lane l = (lane 8i + l / 4, column 8j + 2 (l % 4) + e) of the patch.
 template <int NB> __device__ __forceinline__ void tmem_ld_frag(uint32_t taddr, uint32_t* r) {
   static_assert(NB == 1 || NB == 2 || NB == 4, "column blocks per load");
-#ifdef Q4K_UP_ONLY
-  for (int i = 0; i < 4 * NB; ++i) r[i] = 0;
-  return;
-#endif
   if constexpr (NB == 1) {
     asm volatile("tcgen05.ld.sync.aligned.16x256b.x1.b32 {%0,%1,%2,%3}, [%4];"
                  : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(taddr));
@@ -311,11 +298,6 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     }
   };
 
-#ifdef Q4K_EPI_ONLY
-  uint32_t const up_tiles = 0;
-#else
-  uint32_t const up_tiles = num_tiles;
-#endif
   if (warp < C::kFirstEpilogue) {
   if constexpr (C::kRebalance) {
     static_assert(C::kFirstEpilogue % 4 == 0 && C::kFirstEpilogue * C::kRegsLow + C::kEpilogueWarps * C::kRegsHigh <= C::kWarps * ((65536 / C::kThreads) / 8 * 8),
@@ -323,45 +305,70 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(C::kRegsLow));
   }
   if (warp == kProducerWarp) {
-    // Raw stream: code tiles, metadata, activation scales and sums of every super-block.
+    // One thread feeds both TMA streams: the raw stream (code tiles + metadata of every super-block into the raw
+    // ring) and the activation stream (int8 tiles straight into the operand ring).  It polls the two "slot free"
+    // barriers without blocking on either, so that neither stream ever waits behind the other.
     if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
-        uint32_t row_tile, tok_tile, slice, kb0, kb1;
-        tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
-        int const rg0 = int(row_tile * (kRows / 8));
-        for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
-          uint32_t const r = it % C::kRaw, use = it / C::kRaw;
-          if (!mbar_wait_inline<2048, 256>(bar_raw_free(r), (use & 1) ^ 1, abort_flag, p.status, 1)) { ok = false; break; }
-          uint8_t* const st = smem + C::oRawRing + r * C::kRawStage;
-          uint32_t const bar = bar_raw_full(r);
-          mbar_expect_tx(bar, C::kRawTx);
-          tma_3d(smem_u32(st + C::oRawCodes), &tm_codes, 0, int(kb), rg0, bar);
-          tma_3d(smem_u32(st + C::oRawMeta), &tm_meta, 0, int(kb), rg0, bar);
+      struct Cursor { uint32_t t, kb, kb1, it, row_tile, tok_tile; bool done; };
+      auto open_tile = [&](Cursor& c) {
+        if (c.t >= num_tiles) { c.done = true; return; }
+        uint32_t slice, kb0;
+        tile_coords(c.t, c.row_tile, c.tok_tile, slice, kb0, c.kb1);
+        c.kb = kb0;
+      };
+      auto advance = [&](Cursor& c) {
+        ++c.it;
+        if (++c.kb >= c.kb1) { c.t += gridDim.x; open_tile(c); }
+      };
+      Cursor ra{blockIdx.x, 0, 0, 0, 0, 0, false}, ac = ra;
+      open_tile(ra);
+      open_tile(ac);
+      long long t_last = clock64();
+      uint32_t idle = 0;
+      while (!ra.done || !ac.done) {
+        bool progressed = false;
+        if (!ra.done) {
+          uint32_t const r = ra.it % C::kRaw, use = ra.it / C::kRaw;
+          if (mbar_test(bar_raw_free(r), (use & 1) ^ 1)) {
+            uint8_t* const st = smem + C::oRawRing + r * C::kRawStage;
+            uint32_t const bar = bar_raw_full(r);
+            int const rg0 = int(ra.row_tile * (kRows / 8));
+            mbar_expect_tx(bar, C::kRawTx);
+            tma_3d(smem_u32(st + C::oRawCodes), &tm_codes, 0, int(ra.kb), rg0, bar);
+            tma_3d(smem_u32(st + C::oRawMeta), &tm_meta, 0, int(ra.kb), rg0, bar);
+            advance(ra);
+            progressed = true;
+          }
+        }
+        if (!ac.done) {
+          uint32_t const o = ac.it % C::kOps, use = ac.it / C::kOps;
+          if (mbar_test(bar_op_free(o), (use & 1) ^ 1)) {
+            uint8_t* const st = smem + C::oOps + o * C::kOpStage;
+            uint32_t const bar = bar_b_full(o);
+            int const tok0 = int(ac.tok_tile * NTOK);
+            mbar_expect_tx(bar, C::kBTx);
+            tma_2d(smem_u32(st + C::oB), &tm_act, int(ac.kb) * 256, tok0, bar);
+            tma_2d(smem_u32(st + C::oB + NTOK * 128), &tm_act, int(ac.kb) * 256 + 128, tok0, bar);
+            advance(ac);
+            progressed = true;
+          }
+        }
+        if (progressed) {
+          t_last = clock64();
+          idle = 0;
+        } else if ((++idle & 63u) == 0) {  // bounded like every other wait
+          if (*abort_flag) break;
+          if (clock64() - t_last > kWaitCycles) {
+            *abort_flag = 1;
+            atomicExch(p.status, 1);
+            break;
+          }
         }
       }
-      if (*abort_flag) drain(it > C::kRaw ? it - C::kRaw : 0, it, C::kRaw, bar_raw_full(0));
-    } else if (lane == 1) {
-      // Activation stream (second lane of the same warp; the two lanes progress independently):
-      // int8 tiles straight into the operand ring.
-      uint32_t it = 0;
-      bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
-        uint32_t row_tile, tok_tile, slice, kb0, kb1;
-        tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
-        int const tok0 = int(tok_tile * NTOK);
-        for (uint32_t kb = kb0; kb < kb1; ++kb, ++it) {
-          uint32_t const o = it % C::kOps, use = it / C::kOps;
-          if (!mbar_wait_inline<1024, 256>(bar_op_free(o), (use & 1) ^ 1, abort_flag, p.status, 2)) { ok = false; break; }
-          uint8_t* const st = smem + C::oOps + o * C::kOpStage;
-          uint32_t const bar = bar_b_full(o);
-          mbar_expect_tx(bar, C::kBTx);
-          tma_2d(smem_u32(st + C::oB), &tm_act, int(kb) * 256, tok0, bar);
-          tma_2d(smem_u32(st + C::oB + NTOK * 128), &tm_act, int(kb) * 256 + 128, tok0, bar);
-        }
+      if (*abort_flag) {
+        drain(ra.it > C::kRaw ? ra.it - C::kRaw : 0, ra.it, C::kRaw, bar_raw_full(0));
+        drain(ac.it > C::kOps ? ac.it - C::kOps : 0, ac.it, C::kOps, bar_b_full(0));
       }
-      if (*abort_flag) drain(it > C::kOps ? it - C::kOps : 0, it, C::kOps, bar_b_full(0));
     }
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
@@ -369,7 +376,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       uint64_t const cdesc = umma_desc_sw128(smem_u32(smem + C::oConst), kConstAtomStride);
       uint32_t it = 0;
       bool ok = true;
-      for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
+      for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
         uint32_t row_tile, tok_tile, slice, kb0, kb1;
         tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
         for (uint32_t kb = kb0; ok && kb < kb1; ++kb, ++it) {
@@ -409,7 +416,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     constexpr uint32_t kEntries = (NTOK * 8 + kET - 1) / kET;  // activation-table entries per thread
     uint32_t it = 0;
     bool ok = true;
-    for (uint32_t t = blockIdx.x; ok && t < up_tiles; t += gridDim.x) {
+    for (uint32_t t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
       uint32_t row_tile, tok_tile, slice, kb0, kb1;
       tile_coords(t, row_tile, tok_tile, slice, kb0, kb1);
       uint32_t const tok0 = tok_tile * NTOK;
@@ -424,12 +431,8 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
           uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
           bool const live = j < NTOK * 8 && tok0 + tk < p.m;
           size_t const idx = size_t(tok0 + tk) * p.G + kb * 8 + g;
-#ifndef Q4K_SKIP_ACT
           av[e] = live ? __ldg(p.xscales + idx) : 0.f;
           sv[e] = live ? __ldg(p.xsums + idx) : 0;
-#else
-          av[e] = 0.f; sv[e] = int(live);
-#endif
         }
         if (!mbar_wait_inline<1024, 128>(bar_raw_full(r), (it / C::kRaw) & 1, abort_flag, p.status, 6)) { ok = false; break; }
         if (!mbar_wait_inline<1024, 128>(bar_op_free(o), ((it / C::kOps) & 1) ^ 1, abort_flag, p.status, 7)) { ok = false; break; }
@@ -440,7 +443,6 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         // 1024 raw 16-byte chunks = (row of the tile, K32 group).  A quarter warp takes the eight rows of one
         // 8-row atom, lane i the row i and the group (g0 + i) mod 8: its eight reads and each of its two sets of
         // eight writes fall into eight different 16-byte bank groups.
-#ifndef Q4K_SKIP_EXPAND
         {
           uint32_t const i8 = et & 7;
 #pragma unroll 2
@@ -461,11 +463,9 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             sts128(dst + (((c + 1) ^ i8) << 4), ov[4], ov[5], ov[6], ov[7]);
           }
         }
-#endif
         // Row tables: S = d * sc * 2^100 of every (row, group) and -dmin of every row, laid out so that an epilogue
         // lane finds its four rows (l/4, +8, +16, +24 of its lane quarter) in one 16-byte word; the six-bit mins
         // as bf16, one 16-byte row each (the A operand of the min-term MMA).
-#ifndef Q4K_SKIP_ROWTAB
         for (uint32_t row = et; row < kRows; row += kET) {
           uint4 const cm = lds128(raw + C::oRawMeta + row * 16);
           float const dS = fp16_bits_to_f32(cm.x & 0xffffu) * kRowScalePow, ndmin = -fp16_bits_to_f32(cm.x >> 16);
@@ -483,11 +483,9 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
           sts128(scl + C::oMt + row * 16, mb[0], mb[1], mb[2], mb[3]);
           sts32f(scl + C::oNd + slot * 4, ndmin);
         }
-#endif
         // Activation tables: a' = a * 2^49 per (group, token), and a * sum split into three bf16 terms that add up to
         // it exactly (the B operand of the min-term MMA).  A scale so large that a' is not finite stamps the stage,
         // and the epilogue then works from the plain scales.
-#ifndef Q4K_SKIP_ACT
 #pragma unroll
         for (uint32_t e = 0; e < kEntries; ++e) {
           uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
@@ -505,7 +503,6 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             if (av[e] > kWideAbove) atomicMax(reinterpret_cast<uint32_t*>(smem + C::oSclRing + sc * C::kSclStage + C::oWide), it + 1);
           }
         }
-#endif
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA's async proxy
         __syncwarp();
         if (lane == 0) {
@@ -551,9 +548,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       uint32_t b2, parity2;
       acc_slot<C::kAccBufs>(it2, g2, b2, parity2);
       if (wait_set) {
-#ifndef Q4K_EPI_ONLY
         if (!mbar_wait_inline<512, 128>(bar_acc_full(b2 / C::kMmaPerCommit), parity2, abort_flag, p.status, 10)) return false;
-#endif
         tc_fence_after();
       }
       uint32_t const ta = lane_base + b2 * NTOK + 8 * UB * u;
@@ -575,11 +570,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       for (uint32_t kb = kb0; ok && kb < kb1; ++kb, ++it) {
         uint32_t const sc = it % C::kScl;
         bool const has_next = kb + 1 < kb1 || t + gridDim.x < num_tiles;
-        bool const tr_on = ep == 0 && it >= 6 && it < 8;
-        TRACE_AT(tr_on, 96 + (it - 6) * 3);
-#ifndef Q4K_EPI_ONLY
         if (!mbar_wait_inline<512, 128>(bar_s_full(sc), (it / C::kScl) & 1, abort_flag, p.status, 9)) { ok = false; break; }
-#endif
         uint32_t const scl = smem_s + C::oSclRing + sc * C::kSclStage;
         bool const wide = lds32(scl + C::oWide) == it + 1;
         uint32_t const ssp = scl + C::oS + (quarter * 8 + R0) * 16;  // this lane's four row scales of group g: + g * 512
@@ -587,11 +578,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         // ---- min term of the whole super-block on the tensor cores: rows x groups (six-bit mins, bf16) times
         // groups x tokens (a * sum in three bf16 terms; products exact, fp32 accumulation), scaled by -dmin.
         // (Where the groups are split over several warps, the first of them adds it.)
-#ifdef Q4K_UP_ONLY
-        if (false) {
-#else
         if (GS == 1 || gs == 0) {
-#endif
           uint32_t const mrow = scl + C::oMt + (quarter * 32 + R0) * 16 + q * 4;
           uint32_t const am00 = lds32(mrow), am01 = lds32(mrow + 8 * 16), am10 = lds32(mrow + 16 * 16), am11 = lds32(mrow + 24 * 16);
           float4 const nd4 = lds128f(scl + C::oNd + (quarter * 8 + R0) * 16);
@@ -612,7 +599,6 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             }
           }
         }
-        TRACE_AT(tr_on, 96 + (it - 6) * 3 + 2);
         // ---- one K32 group: tt-th group of this warp in the super-block.  With tt known at compile time (the
         // unrolled fast path) every decision about sets and successors is static and each TMEM read has one site.
         auto group = [&](bool const slow, int const tt) -> bool {
@@ -639,25 +625,19 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             }
 #pragma unroll
             for (int jj = 0; jj < UB; ++jj) Cc[jj] = __fmul2_rn(A[jj], make_float2(kc, kc));
-            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 0);
             tmem_wait_ld();  // this unit has arrived
-            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 1);
             if (u == U - 1) {
               // with its last unit the warp has read all it wants of this group
               if (last_of_set) {  // the set goes back to the MMA warp
                 tc_fence_before();
                 __syncwarp();
-#ifndef Q4K_EPI_ONLY
                 if (lane == 0) mbar_arrive(bar_acc_empty(b / C::kMmaPerCommit));
-#endif
               }
               if (tt + 1 < 8 / GS) got = fetch_unit(nxt, it, g + GS, 0, last_of_set);
               else if (has_next) got = fetch_unit(nxt, it + 1, gs, 0, true);
             } else {
               fetch_unit(nxt, it, g, u + 1, false);
             }
-            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 2);
-#ifndef Q4K_UP_ONLY
             // All first FMAs (a * P * 2^-60), then all second ones (+ (D * 2^60) * that): no FMA waits for its predecessor.
             float2 v[2][2][UB];
 #pragma unroll
@@ -678,8 +658,6 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
 #pragma unroll
                 for (int jj = 0; jj < UB; ++jj) acc[h][u * UB + jj][i2] = __ffma2_rn(s2, v[h][i2][jj], acc[h][u * UB + jj][i2]);
               }
-#endif
-            TRACE_AT(tr_on, (it - 6) * 48 + (tt * U + u) * 4 + 3);
             if (Dump) {
 #pragma unroll
               for (int h = 0; h < 2; ++h)
@@ -708,9 +686,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         }
         if (!ok) break;
         __syncwarp();
-#ifndef Q4K_EPI_ONLY
         if (lane == 0) mbar_arrive(bar_s_free(sc));
-#endif
       }
       if (!ok) break;
 
@@ -862,9 +838,6 @@ cudaError_t launch_ntok(const WeightView& w, const Q8View& x, const TcOutput& o,
   p.out_bf16 = o.out_bf16; p.ndst = o.ndst; p.out_stride = o.stride ? o.stride : w.n; p.out_row0 = o.row0;
   p.partials = partials; p.partial_tiles = partial_tiles; p.tickets = tickets; p.status = status;
   p.n = w.n; p.m = x.m; p.tiles_k = w.tiles_k; p.split_k = split_k; p.G = uint32_t(G); p.row_tiles = row_tiles; p.tok_tiles = tok_tiles;
-#ifdef Q4K_TC_TRACE
-  if (const char* e = getenv("Q4K_TC_TRACE")) p.trace = reinterpret_cast<long long*>(strtoull(e, nullptr, 16));
-#endif
   uint64_t const tiles = uint64_t(row_tiles) * tok_tiles * split_k;
   uint32_t const grid = uint32_t(tiles < uint64_t(sm_count()) ? tiles : uint64_t(sm_count()));
   kernel<<<grid, C::kThreads, C::kSmem, stream>>>(tm_codes, tm_meta, tm_act, p);

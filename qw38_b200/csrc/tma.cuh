@@ -27,6 +27,13 @@ __device__ __forceinline__ bool mbar_try(uint32_t bar, uint32_t parity) {
                : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
   return ok != 0;
 }
+// One look at the barrier, never blocking.
+__device__ __forceinline__ bool mbar_test(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{ .reg .pred p; mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p; }"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
 // Slow path of a bounded wait.
 __device__ __forceinline__ bool mbar_wait_spin(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   long long const t0 = clock64();
@@ -51,24 +58,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (mbar_try(bar, parity)) return true;
   return mbar_wait_slow(bar, parity, abort_flag, status, code);
 }
-// Bounded wait for kernels in which many warps wait at once next to warps that compute: a waiting warp must not
-// take issue slots from the working ones, so between two tries it sleeps (FirstNs, doubling up to MaxNs) instead
-// of spinning; the abort flag and the clock are looked at every eighth try.  Fully inlined: a function call inside
-// a kernel that moves registers between warps with setmaxnreg does not compile.
+// The same wait, fully inlined: a function call inside a kernel that moves registers between warps with setmaxnreg
+// does not compile.  mbarrier.try_wait suspends the thread in hardware for a while by itself; sleeping between tries
+// (nanosleep, any back-off) only added wake-up latency to the hand-offs when it was measured, so there is none.  The
+// abort flag and the clock are looked at every eighth try.  (The template arguments are kept for the call sites.)
 template <uint32_t MaxNs = 256, uint32_t FirstNs = 32>
 __device__ __forceinline__ bool mbar_wait_inline(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status, int code) {
   if (mbar_try(bar, parity)) return true;
   long long const t0 = clock64();
-#ifndef Q4K_WAIT_SCALE
-#define Q4K_WAIT_SCALE 1
-#endif
-  uint32_t ns = FirstNs * Q4K_WAIT_SCALE;
   for (uint32_t tries = 1;; ++tries) {
-#ifdef Q4K_WAIT_SLEEP
-    __nanosleep(ns);
-#endif
     if (mbar_try(bar, parity)) return true;
-    if (ns < MaxNs * Q4K_WAIT_SCALE) ns *= 2;
     if ((tries & 7u) == 0) {
       if (*abort_flag) return false;
       if (clock64() - t0 > kWaitCycles) {
