@@ -326,11 +326,15 @@ def main():
         out_group[parity] = pool[start:off]
 
     def projection(m, i, layer, parity):
+        # Both activation packs of a layer are enqueued before its four projections, so no projection's input is
+        # written by the launch directly before it: the projections may run into each other (input_settled).
         _, n, k = SHAPES[i]
+        settled = not args.no_overlap
         if fused:
-            q4k_q8_project_gather(layers[layer][i], q8[(m, k)], out_ptrs[(parity, m, i)], flag_ptrs, rank, shard(n)[0], n)
+            q4k_q8_project_gather(layers[layer][i], q8[(m, k)], out_ptrs[(parity, m, i)], flag_ptrs, rank, shard(n)[0], n,
+                                  input_settled=settled)
         else:
-            q4k_q8_project(layers[layer][i], q8[(m, k)], out=outs[(parity, m, i)], trusted=True)
+            q4k_q8_project(layers[layer][i], q8[(m, k)], out=outs[(parity, m, i)], trusted=True, input_settled=settled)
 
     def stream_step(parity, quantise=True, only_m=None, wait=True):
         for m in tokens:
@@ -491,7 +495,7 @@ def main():
                            "parallelism": f"rows/{world}" + (" + peer stores fused into the projection kernels, one bounded "
                                                                      "cross-GPU wait per step" if fused else ""),
                            "launch": ("eager" if args.no_graph else "CUDA graph replay, one graph per step") +
-                                     ("" if args.no_overlap else ", programmatic dependent launch (decode kernels)"),
+                                     ("" if args.no_overlap else ", programmatic dependent launch (every kernel of the step; projections flagged input_settled)"),
                            "bytes_per_step": total_bytes, "parity_check": checked},
                 "clocks": clocks, "gpu_launches": launches_per_step * steps,
                 "e2e": {"value": e2e_value, "unit": "GB/s", "h2d_bytes_per_step": x_words * 2,

@@ -88,6 +88,13 @@ typedef struct q4k_project_options {
 /* Skip the per-call device-span checks (pointer attributes, allocation bounds); geometry
  * and overlap checks still run.  For callers that validated the same buffers once. */
 #define Q4K_FLAG_TRUSTED_SPANS 1u
+/* With launch overlap on (q4k_set_launch_overlap): the activations (codes, scales, sums) and the residual of this
+ * call were NOT written by the launch directly before it on the stream -- they were complete before that launch
+ * was enqueued.  The tcgen05 kernel (m > 16) then starts on SMs the preceding launch leaves idle and computes
+ * while it drains, waiting for it only before its first store; without the flag it prefetches weights and waits
+ * before it reads activations.  Every kernel of this library lets its successor start only once its own
+ * predecessor has completed, so "not the launch directly before" is all the caller has to know. */
+#define Q4K_FLAG_INPUT_SETTLED 2u
 
 const char* q4k_last_error(void);   /* thread-local text of the last failure */
 int q4k_last_cuda_status(void);     /* cudaError_t of the last Q4K_ERR_STATUS */
@@ -161,13 +168,24 @@ int q4k_prefill_paired_swiglu(const q4k_weight* gate, const q4k_weight* up, cons
  * may be read.  `outputs` and `row_offset`/`total_rows` of the descriptor are not used by the wait.  The
  * wait gives up after limit_cycles SM clocks (0 = about two seconds) and then sets the status word of
  * q4k_kernel_status.  q4k_peer_announce does the announcement alone (a rank that has other work to enqueue
- * before it needs the peers' rows).  All ranks must enqueue the same sequence of gather projections. */
+ * before it needs the peers' rows).  All ranks must enqueue the same sequence of gather projections.
+ * m <= 16 runs the TMA-fed decode kernel, larger m (up to Q4K_MAX_TOKENS) the tcgen05 kernel; both store to the peers.
+ *
+ * Reuse of a gathered buffer: the protocol proves DELIVERY, not consumption.  When q4k_peer_wait returns on rank A
+ * every peer has delivered step t, but a peer may still be reading its copy of the step-t outputs; A's next gather
+ * projection into the same buffer would overwrite them.  A buffer may be written again only after every rank has
+ * passed one more q4k_peer_wait since it last read the buffer.  In practice: alternate two sets of gathered outputs
+ * by step parity (one wait per step then suffices, because a rank that stores step t+2 has passed the wait of
+ * step t+1, and a peer's step t+1 projections run after its reads of step t when those are ordered before them
+ * in the stream), as bench.py does.
+ * A projection whose kernel gave up on a bounded wait (status word nonzero) is not counted as delivered. */
 typedef struct q4k_gather_desc {
   float* outputs[8];    /* outputs[g]: rank g's buffer as addressable from this process */
   uint32_t* flags[8];   /* flags[g]: rank g's uint32[16] flag array as addressable from this process; start zeroed */
   uint32_t ranks, rank;
   uint32_t row_offset;  /* first output row of this rank's shard; a multiple of 8 */
   uint32_t total_rows;  /* N of the whole matrix */
+  uint32_t options;     /* Q4K_FLAG_INPUT_SETTLED or 0 */
 } q4k_gather_desc;
 int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gather_desc* desc,
                           const float* residual, uint64_t residual_len, void* stream);

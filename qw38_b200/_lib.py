@@ -40,13 +40,14 @@ class DecodeDesc(C.Structure):
                 ("epilogue", C.c_uint8), ("activation_policy", C.c_uint8)]
 
 
+FLAG_TRUSTED_SPANS, FLAG_INPUT_SETTLED = 1, 2
 EPILOGUE_STORE_BF16, EPILOGUE_STORE_FP32, EPILOGUE_RESIDUAL_ADD_FP32, EPILOGUE_SWIGLU_STORE_BF16 = 1, 2, 3, 4
 ACTIVATION_BF16, ACTIVATION_Q8_K32 = 1, 2
 
 
 class GatherDesc(C.Structure):
     _fields_ = [("outputs", C.c_void_p * 8), ("flags", C.c_void_p * 8), ("ranks", C.c_uint32), ("rank", C.c_uint32),
-                ("row_offset", C.c_uint32), ("total_rows", C.c_uint32)]
+                ("row_offset", C.c_uint32), ("total_rows", C.c_uint32), ("options", C.c_uint32)]
 
 
 _u32, _u64, _vp, _i = C.c_uint32, C.c_uint64, C.c_void_p, C.c_int

@@ -218,7 +218,7 @@ int caller_scratch(const q4k_project_options* opt, uint64_t partial_bytes, uint6
   return Q4K_OK;
 }
 
-constexpr uint32_t kFlagTrustedSpans = 1u;
+constexpr uint32_t kFlagTrustedSpans = 1u, kFlagInputSettled = 2u;
 
 int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output, uint64_t output_len,
                  const float* residual, uint64_t residual_len, const q4k_project_options* opt,
@@ -311,7 +311,9 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
     }
     int* status = q4k::kernel_status_word();
     if (!status) return Q4K_ERR_STATUS;
-    Q4K_CUDA(q4k::launch_mmq_tcgen05(view(w), view(x), q4k::tc_output(output, res), partials, plan,
+    q4k::TcOutput tc = q4k::tc_output(output, res);
+    tc.input_settled = (opt && (opt->flags & kFlagInputSettled)) ? 1u : 0u;
+    Q4K_CUDA(q4k::launch_mmq_tcgen05(view(w), view(x), tc, partials, plan,
                                      static_cast<uint8_t*>(scratch) + kTicketRegion, static_cast<uint32_t*>(scratch),
                                      status, stream),
              "q4k_q8.mmq_tcgen05");
@@ -496,6 +498,7 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
   out.residual = residual_len ? residual : nullptr;
   out.ndst = desc->ranks; out.stride = desc->total_rows; out.row0 = desc->row_offset;
   out.done = done; out.unsignalled = unsignalled; out.rank = desc->rank;
+  out.input_settled = (desc->options & kFlagInputSettled) ? 1u : 0u;
   Q4K_CUDA(q4k::launch_mmq_tcgen05(view(w), view(x), out, nullptr, plan, base + kTicketRegion, reinterpret_cast<uint32_t*>(base),
                                    status, stream),
            "q4k_q8.mmq_tcgen05_gather");

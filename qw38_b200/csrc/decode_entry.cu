@@ -20,8 +20,8 @@ __device__ __forceinline__ float sigmoid_fp32(float u) {
 }
 
 __global__ void store_bf16_kernel(const float* __restrict__ in, uint16_t* __restrict__ out, uint64_t count) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();  // after the wait: the next launch never runs beside anything older than this one
   uint64_t const i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) out[i] = f32_to_bf16_rne(in[i]);
 }
@@ -29,8 +29,8 @@ __global__ void store_bf16_kernel(const float* __restrict__ in, uint16_t* __rest
 // y = bf16(SiLU(gate) * up)  (SwigluStoreBf16, cuda/decode_mmv.cu:238-242)
 __global__ void swiglu_store_bf16_kernel(const float* __restrict__ gate, const float* __restrict__ up,
                                          uint16_t* __restrict__ out, uint64_t count) {
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();  // after the wait: the next launch never runs beside anything older than this one
   uint64_t const i = uint64_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i < count) {
     float const g = gate[i];

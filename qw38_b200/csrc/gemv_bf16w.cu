@@ -23,8 +23,8 @@ __global__ void __launch_bounds__(kThreads) gemv_bf16w_kernel(WeightView w, cons
                                                              uint32_t padded_k, float* __restrict__ out,
                                                              const float* __restrict__ residual) {
   extern __shared__ __align__(16) float xs[];  // [M][padded_k], zero beyond k
-  pdl_launch_dependents();
   pdl_wait();
+  pdl_launch_dependents();  // after the wait: the next launch never runs beside anything older than this one
   for (uint32_t i = threadIdx.x; i < M * padded_k; i += kThreads) {
     uint32_t const t = i / padded_k, c = i % padded_k;
     xs[i] = c < k ? bf16_bits_to_f32(x[size_t(t) * k + c]) : 0.f;

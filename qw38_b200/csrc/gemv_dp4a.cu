@@ -71,8 +71,8 @@ __global__ void __launch_bounds__(kThreads) gemv_dp4a_kernel(WeightView w, Q8Vie
                                                              const float* __restrict__ residual,
                                                              int32_t* __restrict__ partials, uint32_t rgc, bool wide) {
   extern __shared__ __align__(16) uint8_t smem[];
-  pdl_launch_dependents();
   pdl_wait();  // activations (and the residual) may come from the kernel before this one
+  pdl_launch_dependents();  // after the wait: the next launch never runs beside anything older than this one
   uint32_t const pk = x.padded_k, G = pk / 32, tiles_k = w.tiles_k;
   uint8_t* const zs = smem;
   float* const as = reinterpret_cast<float*>(smem + size_t(M) * tiles_k * kActKb);

@@ -161,7 +161,6 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
   uint32_t const t1 = min(p.row_tiles, t0 + p.tiles_per_range);
   uint32_t const ntiles = t1 > t0 ? t1 - t0 : 0;
 
-  pdl_launch_dependents();
   if (threadIdx.x == 0) {
     for (uint32_t s = 0; s < stages; ++s) {
       mbar_init(b_full + 8 * s, 1);
@@ -207,6 +206,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
     uint32_t const nt = warp - kFirstReducer;
     uint32_t const r = lane >> 2, q = lane & 3;
     pdl_wait();
+    pdl_launch_dependents();  // after the wait: the next launch never runs beside anything older than this one
     if (p.done != nullptr && blockIdx.x == 0 && warp == kFirstReducer && lane == 0) announce_deliveries(p.unsignalled, p.peer_flag, p.ndst, p.rank);
     // Destination of this warp's values: the K slice's scratch tile, or the output (one buffer, or every
     // rank's copy of the gathered output).  Offsets are those of (tok0, row 0).

@@ -75,6 +75,7 @@ struct TcOutput {
   uint32_t* done;
   uint32_t* unsignalled;
   uint32_t rank;
+  uint32_t input_settled;  // Q4K_FLAG_INPUT_SETTLED: activations and residual do not come from the launch directly before
 };
 inline TcOutput tc_output(float* out, const float* residual) {
   TcOutput o{};

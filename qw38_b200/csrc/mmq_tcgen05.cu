@@ -43,10 +43,11 @@
 //               map, 128-byte swizzle, rows beyond m zero-filled) into the operand ring;
 //   warp 1      allocates TMEM; one lane issues, set by set, the constant MMAs and the data MMAs
 //               into the set's accumulator buffers, then tcgen05.commit;
-//   expanders   (6 or 10 warps) expand nibbles to int8 in the K-major 128-byte-swizzled operand
+//   expanders   (5 or 9 warps) expand nibbles to int8 in the K-major 128-byte-swizzled operand
 //               layout, decode the six-bit scales into the row tables (S, -dmin, mins as bf16)
 //               and build the token tables (a', a * sum in three bf16 terms) from the
 //               activations' scales and sums in global memory;
+//   one warp    waits for the launch before this one (griddepcontrol.wait) and then releases the next one;
 //   epilogue    tiles of 128 tokens: 16 warps, four column quarters per TMEM lane quarter; 64
 //               tokens: 8 warps, two column halves; narrower tiles split the eight K32 groups
 //               over two warps per lane quarter and add their sums in warp order at the end of
@@ -96,13 +97,14 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kEpilogueWarps = 4 * kColSplit * kGroupSplit;
   // Roles are aligned to groups of four warps (the register file is shared by the four warps that sit
   // on one scheduler each): producer + MMA + expanders fill the first groups, the epilogue the rest.
-  static constexpr int kExpanders = NTOK >= 64 ? 6 : 10;  // measured: more expander warps on the wide tiles slow the block down
+  static constexpr int kExpanders = NTOK >= 64 ? 5 : 9;  // measured: more expander warps on the wide tiles slow the block down
+  static constexpr int kDepWarp = kFirstExpander + kExpanders;  // waits for the preceding launch, releases the next one
   // Wide tiles: the non-epilogue warps give registers back, the epilogue warps take them (setmaxnreg).
   static constexpr bool kRebalance = NTOK >= 128 || NTOK == 32;
   // The block's own allocation is the pool: 24 warps start at 80 registers (8 * 48 + 16 * 96 = 24 * 80), 28 warps at 72
   // (12 * 48 + 16 * 88 <= 28 * 72).  Asking for more than the pool holds blocks the warps forever.
   static constexpr int kRegsLow = 48;
-  static constexpr int kFirstEpilogue = kFirstExpander + kExpanders;
+  static constexpr int kFirstEpilogue = kDepWarp + 1;
   static constexpr int kWarps = kFirstEpilogue + kEpilogueWarps;
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8 > 128 ? 128 : (65536 / kThreads) / 8 * 8;
@@ -167,6 +169,7 @@ struct TcParams {
   uint32_t* tickets;
   int* status;
   uint32_t n, m, tiles_k, split_k, G, row_tiles, tok_tiles;
+  uint32_t input_settled;  // activations and residual were complete before the preceding launch was enqueued
 };
 
 // Accumulator patch of 16 TMEM lanes x (8 * NB) columns in the MMA C-fragment layout: register
@@ -275,9 +278,13 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
   __syncthreads();
   tc_fence_after();
   uint32_t const tmem_base = *tmem_slot;
-  // Row-sharded use: the projections that finished before this launch are announced to the peers now (their
-  // grids have completed, so their stores into the peers' buffers are visible).
-  if (p.done != nullptr && blockIdx.x == 0 && threadIdx.x == 0) announce_deliveries(p.unsignalled, p.peer_flag, p.ndst, p.rank);
+  // Launched with programmatic stream serialization the block may be running while the launch before it
+  // drains.  Weights never depend on that launch.  Everything else does, unless the caller said otherwise
+  // (input_settled: activations and residual are older): each role executes griddepcontrol.wait before its first
+  // access to such memory -- activations (producer, expanders), outputs, residual, split-K scratch, tickets and
+  // the gather's counters (epilogue, at the end of its first tile).  One lane per block waits for the preceding
+  // launch on the block's behalf and only then lets the NEXT launch start (launch_dependents): a successor thus
+  // never runs beside anything older than its direct predecessor.
 
   auto tile_coords = [&](uint32_t t, uint32_t& row_tile, uint32_t& tok_tile, uint32_t& slice, uint32_t& kb0, uint32_t& kb1) {
     tok_tile = t % p.tok_tiles;  // token tile fastest: blocks running together share weight tiles in L2
@@ -309,6 +316,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     // ring) and the activation stream (int8 tiles straight into the operand ring).  It polls the two "slot free"
     // barriers without blocking on either, so that neither stream ever waits behind the other.
     if (lane == 0) {
+      bool deps_ok = p.input_settled != 0;
       struct Cursor { uint32_t t, kb, kb1, it, row_tile, tok_tile; bool done; };
       auto open_tile = [&](Cursor& c) {
         if (c.t >= num_tiles) { c.done = true; return; }
@@ -340,7 +348,11 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
             progressed = true;
           }
         }
-        if (!ac.done) {
+        if (!ac.done && !deps_ok && !progressed) {  // the raw ring is full (or done): now the activations are needed
+          pdl_wait();
+          deps_ok = true;
+        }
+        if (!ac.done && deps_ok) {
           uint32_t const o = ac.it % C::kOps, use = ac.it / C::kOps;
           if (mbar_test(bar_op_free(o), (use & 1) ^ 1)) {
             uint8_t* const st = smem + C::oOps + o * C::kOpStage;
@@ -370,6 +382,14 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         drain(ac.it > C::kOps ? ac.it - C::kOps : 0, ac.it, C::kOps, bar_b_full(0));
       }
     }
+  } else if (warp == C::kDepWarp) {
+    // Waits for the launch before this one on the block's behalf (a warp of its own: the wait may last as long as
+    // that launch does), then lets the next launch start.
+    pdl_wait();
+    pdl_launch_dependents();
+    // Row-sharded use: the projections that finished before this launch are announced to the peers now (their
+    // grids have completed, so their stores into the peers' buffers are visible).
+    if (p.done != nullptr && blockIdx.x == 0 && lane == 0) announce_deliveries(p.unsignalled, p.peer_flag, p.ndst, p.rank);
   } else if (warp == kMmaWarp) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc_i8(NTOK);
@@ -411,6 +431,7 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       }
     }
   } else {
+    if (!p.input_settled) pdl_wait();  // the activations' scales and sums are read from global memory
     uint32_t const et = threadIdx.x - kFirstExpander * 32;  // 0 .. 32*kExpanders-1
     constexpr uint32_t kET = C::kExpanders * 32;
     constexpr uint32_t kEntries = (NTOK * 8 + kET - 1) / kET;  // activation-table entries per thread
@@ -525,6 +546,8 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
     bool const final_warp = gs == 0;               // holds the tile's sums after the group-split reduction
     uint32_t it = 0, ep_phase = 0;
     bool ok = true;
+    bool deps_ok = !p.input_settled || Dump;  // otherwise the wait comes at the end of the first tile
+    if (deps_ok) pdl_wait();
     auto ep_sync = [&](int code) {  // all epilogue warps meet (bounded like every other wait)
       __syncwarp();
       if (lane == 0) mbar_arrive(bar_ep);
@@ -691,6 +714,10 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       if (!ok) break;
 
       // ---- end of tile: combine the group-split warps, then write (or hand to the split-K fix-up)
+      if (!deps_ok) {  // outputs, residual, scratch and tickets may still belong to the launch before this one
+        pdl_wait();
+        deps_ok = true;
+      }
       auto value = [&](int v) -> float& {
         float2& a2 = acc[v / (4 * NB)][(v / 4) % NB][(v >> 1) & 1];
         return (v & 1) ? a2.y : a2.x;
@@ -837,11 +864,11 @@ cudaError_t launch_ntok(const WeightView& w, const Q8View& x, const TcOutput& o,
   for (uint32_t g = 0; g < 8; ++g) p.out[g] = g < o.ndst ? o.out[g] : nullptr;
   p.out_bf16 = o.out_bf16; p.ndst = o.ndst; p.out_stride = o.stride ? o.stride : w.n; p.out_row0 = o.row0;
   p.partials = partials; p.partial_tiles = partial_tiles; p.tickets = tickets; p.status = status;
+  p.input_settled = o.input_settled;
   p.n = w.n; p.m = x.m; p.tiles_k = w.tiles_k; p.split_k = split_k; p.G = uint32_t(G); p.row_tiles = row_tiles; p.tok_tiles = tok_tiles;
   uint64_t const tiles = uint64_t(row_tiles) * tok_tiles * split_k;
   uint32_t const grid = uint32_t(tiles < uint64_t(sm_count()) ? tiles : uint64_t(sm_count()));
-  kernel<<<grid, C::kThreads, C::kSmem, stream>>>(tm_codes, tm_meta, tm_act, p);
-  return cudaGetLastError();
+  return launch_kernel(kernel, grid, C::kThreads, C::kSmem, stream, launch_overlap(), tm_codes, tm_meta, tm_act, p);
 }
 
 }  // namespace

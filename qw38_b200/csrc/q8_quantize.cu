@@ -70,8 +70,9 @@ template <typename T, bool Vec>
 __global__ void __launch_bounds__(kThreads) pack_kernel(const T* __restrict__ in, int8_t* codes,
                                                          float* scales, int32_t* sums, uint32_t m,
                                                          uint32_t k, uint32_t pk, int* failure) {
-  pdl_launch_dependents();  // the projection that follows may start prefetching its weights
   pdl_wait();               // the input may come from the kernel before this one
+  pdl_launch_dependents();  // the projection that follows may start prefetching its weights (after the wait: the
+                            // next launch never runs beside anything older than this one)
   uint32_t const lane = threadIdx.x & 31, sub = lane & 3, grp = lane >> 2;
   uint64_t const chunks_row = pk / 256;
   uint64_t const tasks = uint64_t(m) * chunks_row;

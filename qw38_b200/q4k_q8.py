@@ -146,13 +146,14 @@ def pack_q8(x: torch.Tensor, failure: torch.Tensor, out: Optional[Q8Input] = Non
 def q4k_q8_project(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor] = None,
                    residual: Optional[torch.Tensor] = None, *, kernel: int = L.KERNEL_AUTO, split_k: int = 0,
                    row_groups: int = 0, partials: Optional[torch.Tensor] = None, workspace: Optional[torch.Tensor] = None,
-                   trusted: bool = False, stream=None) -> torch.Tensor:
-    """q4k_q8_project (cuda/q4k_q8.hpp:35-37): fp32 out[token, row], token-major."""
+                   trusted: bool = False, input_settled: bool = False, stream=None) -> torch.Tensor:
+    """q4k_q8_project (cuda/q4k_q8.hpp:35-37): fp32 out[token, row], token-major.
+    `input_settled`: Q4K_FLAG_INPUT_SETTLED (x and residual were not written by the launch directly before)."""
     lib = L.load()
     if out is None:
         out = torch.empty((x.m, weight.n), dtype=torch.float32, device=x.codes.device)
     w = weight.c_struct()
-    plain = kernel == L.KERNEL_AUTO and split_k == 0 and row_groups == 0 and partials is None and workspace is None and not trusted
+    plain = kernel == L.KERNEL_AUTO and split_k == 0 and row_groups == 0 and partials is None and workspace is None and not trusted and not input_settled
     if plain:
         _check(lib.q4k_q8_project(C.byref(w), x.c_struct(), _ptr(out), out.numel(), _ptr(residual),
                                   0 if residual is None else residual.numel(), _stream(stream)))
@@ -161,7 +162,7 @@ def q4k_q8_project(weight: PrefillWeight, x: Q8Input, out: Optional[torch.Tensor
                                0 if partials is None else partials.numel(),
                                0 if workspace is None else workspace.data_ptr(),
                                0 if workspace is None else workspace.numel() * workspace.element_size(),
-                               L.FLAG_TRUSTED_SPANS if trusted else 0)
+                               (L.FLAG_TRUSTED_SPANS if trusted else 0) | (L.FLAG_INPUT_SETTLED if input_settled else 0))
         _check(lib.q4k_q8_project_ex(C.byref(w), x.c_struct(), _ptr(out), out.numel(), _ptr(residual),
                                      0 if residual is None else residual.numel(), C.byref(opt), _stream(stream)))
     return out
@@ -204,15 +205,18 @@ def q4k_q8_project_ragged(weight: PrefillWeight, x: Q8Input, row_offsets: Sequen
 
 
 def q4k_q8_project_gather(shard: PrefillWeight, x: Q8Input, outputs: Sequence[int], flags: Sequence[int], rank: int,
-                          row_offset: int, total_rows: int, residual: Optional[torch.Tensor] = None, stream=None) -> None:
+                          row_offset: int, total_rows: int, residual: Optional[torch.Tensor] = None, stream=None,
+                          input_settled: bool = False) -> None:
     """Row-sharded decode projection with the gather fused in (q4k_q8_project_gather): `outputs[g]` /
     `flags[g]` are rank g's full [m, total_rows] fp32 buffer and zeroed uint32[16] flag array as device addresses
-    valid in this process.  This rank's rows land in every buffer; flags[g][rank] is then incremented."""
+    valid in this process.  This rank's rows land in every buffer; flags[g][rank] is then incremented.
+    `input_settled`: Q4K_FLAG_INPUT_SETTLED (x and residual were not written by the launch directly before)."""
     desc = L.GatherDesc()
     for g, (o, f) in enumerate(zip(outputs, flags)):
         desc.outputs[g] = int(o)
         desc.flags[g] = int(f)
     desc.ranks, desc.rank, desc.row_offset, desc.total_rows = len(outputs), rank, row_offset, total_rows
+    desc.options = L.FLAG_INPUT_SETTLED if input_settled else 0
     _check(L.load().q4k_q8_project_gather(C.byref(shard.c_struct()), x.c_struct(), C.byref(desc), _ptr(residual),
                                           0 if residual is None else residual.numel(), _stream(stream)))
 
