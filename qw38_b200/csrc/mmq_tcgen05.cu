@@ -889,15 +889,19 @@ TcPlan plan_tcgen05(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_r
     // Pick the K split with the shortest estimated time, in units of one super-block step of a block: a block
     // pays its pipeline fill once, and per tile the K walk plus the tile end (longer with split-K: partial tiles
     // go through global scratch and the last block of a tile adds them).  Measured on 64-token tiles: fill ~1.7,
-    // tile end ~1, split-K tile end ~2.5 steps.  Slices keep at least four super-blocks.
+    // tile end ~1, split-K tile end ~2.5 steps.  Slices keep at least four super-blocks.  With launch overlap on,
+    // SMs a launch leaves idle are taken by the next launch, so splitting K to fill them buys less: the extra
+    // tile ends are then charged at 5 steps (measured on the 64-layer stream: 4 to 8 give the same plans, and
+    // 7 % more throughput than 2.5; 12 and "never split" lose).
     uint32_t const sms = uint32_t(sm_count());
+    double const split_end = launch_overlap() ? 5.0 : 2.5;
     uint32_t const max_split = tiles_k / 4 ? (tiles_k / 4 > 16 ? 16 : tiles_k / 4) : 1;
     double best = 1e30;
     split = 1;
     for (uint32_t s = 1; s <= max_split; ++s) {
       uint64_t const tiles = uint64_t(blocks) * s;
       uint64_t const rounds = (tiles + sms - 1) / sms;
-      double const cost = 1.7 + double(rounds) * ((s > 1 ? 2.5 : 1.0) + double((tiles_k + s - 1) / s));
+      double const cost = 1.7 + double(rounds) * ((s > 1 ? split_end : 1.0) + double((tiles_k + s - 1) / s));
       if (cost < best - 1e-9) { best = cost; split = s; }
     }
   }
