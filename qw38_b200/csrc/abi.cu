@@ -289,6 +289,7 @@ int project_impl(const q4k_weight* weight, const q4k_q8_input& x, float* output,
     }
     int* status = q4k::kernel_status_word();
     if (!status) return Q4K_ERR_STATUS;
+    plan.input_settled = (opt && (opt->flags & kFlagInputSettled)) ? 1u : 0u;
     Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), output, res, partials, plan,
                                   static_cast<uint8_t*>(scratch) + kTicketRegion, static_cast<uint32_t*>(scratch),
                                   status, stream),
@@ -481,6 +482,7 @@ int q4k_q8_project_gather(const q4k_weight* shard, q4k_q8_input x, const q4k_gat
     gather.unsignalled = unsignalled;
     gather.done = done;
     gather.ranks = desc->ranks; gather.rank = desc->rank; gather.row_offset = desc->row_offset; gather.total_rows = desc->total_rows;
+    plan.input_settled = (desc->options & kFlagInputSettled) ? 1u : 0u;
     Q4K_CUDA(q4k::launch_gemv_tma(view(w), view(x), nullptr, residual_len ? residual : nullptr, nullptr, plan,
                                   base + kTicketRegion, reinterpret_cast<uint32_t*>(base), status, stream, &gather),
              "q4k_q8.gemv_tma_gather");

@@ -82,6 +82,7 @@ struct GtParams {
   // whose 16-row tiles alternate and whose result is bf16(SiLU(gate) * up)).  nseg == 0: the plain form above.
   GtSegment seg[3];
   uint32_t nseg, pair, n_total;  // n_total: rows of all segments = row stride of the split-K scratch
+  uint32_t input_settled;        // activations were complete before the preceding launch was enqueued
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -328,7 +329,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
   } else if (warp - kFirstConsumer < nact) {
     uint32_t const w = warp - kFirstConsumer, sb = sb0 + w;
     uint32_t const r = lane >> 2, q = lane & 3;
-    pdl_wait();
+    if (!p.input_settled || p.partials != nullptr) pdl_wait();  // activations; the reducer waits before anything is stored
     // ---- K-stationary operands ----
     uint32_t const tab = s_tab + w * tab_bytes;
     // activation scale pairs {a[2q], a[2q+1]} of (octet nt, group g) at ((nt*4 + g/2)*4 + q)*16 + (g%2)*8
@@ -683,6 +684,7 @@ cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, co
   p.n = w.n; p.m = x.m; p.padded_k = x.padded_k; p.tiles_k = w.tiles_k; p.G = x.padded_k / 32;
   p.row_tiles = (w.padded_n + 15) / 16; p.cw = cw; p.split_k = plan.split_k;
   p.tiles_per_range = plan.tiles_per_range; p.stages = plan.stages; p.red_slots = plan.red_slots;
+  p.input_settled = plan.input_settled;
   uint32_t const grid = plan.ranges * plan.split_k, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
   bool const dump = partials != nullptr;
   return launch_by_shape(nt, cw, t, p, dump, grid, smem, stream);
@@ -715,6 +717,7 @@ cudaError_t launch_gemv_tma_multi(const WeightView* ws, const GemvTmaOutput* out
   p.n = ws[0].n; p.m = x.m; p.padded_k = x.padded_k; p.tiles_k = ws[0].tiles_k; p.G = x.padded_k / 32;
   p.row_tiles = total_tiles; p.cw = cw; p.split_k = plan.split_k;
   p.tiles_per_range = plan.tiles_per_range; p.stages = plan.stages; p.red_slots = plan.red_slots;
+  p.input_settled = plan.input_settled;
   p.nseg = count; p.pair = swiglu_pair ? 1u : 0u; p.n_total = total_rows;
   uint32_t const grid = plan.ranges * plan.split_k, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
   return launch_by_shape(nt, cw, t, p, false, grid, smem, stream);

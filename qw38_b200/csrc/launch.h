@@ -100,6 +100,7 @@ struct GemvTmaPlan {
   uint32_t ranges, tiles_per_range;  // row ranges (blocks per slice) and 16-row tiles per range
   uint32_t stages;   // depth of the weight ring
   uint32_t red_slots;  // hand-off buffers between consumers and reducer: 1 or 2
+  uint32_t input_settled = 0;  // Q4K_FLAG_INPUT_SETTLED: the consumer warps load activations without waiting for the preceding launch
 };
 bool gemv_tma_supported(const WeightView& w, const Q8View& x);
 GemvTmaPlan plan_gemv_tma(uint32_t m, uint32_t n, uint32_t tiles_k, uint32_t split_k_request, uint32_t warps_request);
