@@ -1083,7 +1083,20 @@ int q4k_q8_mlp(const q4k_weight* gate, const q4k_weight* up, const q4k_weight* d
     cudaError_t st = cudaMemsetAsync(failure, 0, 4, stream);
     if (st != cudaSuccess) return bail(fail_cuda(st, "q8.clear_failure"));
   }
-  q4k_q8_input xh{codes, scales, sums, uint64_t(m) * hidden, uint64_t(m) * (hidden / 32), uint64_t(m) * (hidden / 32), m, hidden, hidden};
+  // Up to sixteen tokens with TMA-able gate / up weights whose K fits one block: the gate projection, the up
+  // projection and the SwiGLU -> Q8 pack run as ONE launch (three launches for the chain instead of five).  That
+  // launch reads the hidden activation while it writes the ffn activation, so the hidden activation moves out of
+  // the shared region into the (then unused) fp32 gate rows.
+  q4k::GemvTmaPlan fused_plan{};
+  q4k::Q8View probe{};
+  probe.m = m;
+  probe.codes = reinterpret_cast<const int8_t*>(g);
+  bool const fused = m <= q4k::kGemvTmaMaxTokens && q4k::gemv_tma_supported(view(*gate), probe) &&
+                     q4k::gemv_tma_supported(view(*up), probe) && q4k::plan_gemv_tma_swiglu_q8(m, view(*gate), &fused_plan);
+  int8_t* const hcodes = fused ? reinterpret_cast<int8_t*>(g) : codes;
+  float* const hscales = fused ? reinterpret_cast<float*>(hcodes + uint64_t(m) * hidden) : scales;
+  int32_t* const hsums = fused ? reinterpret_cast<int32_t*>(hscales + uint64_t(m) * (hidden / 32)) : sums;
+  q4k_q8_input xh{hcodes, hscales, hsums, uint64_t(m) * hidden, uint64_t(m) * (hidden / 32), uint64_t(m) * (hidden / 32), m, hidden, hidden};
   q4k_q8_input xf{codes, scales, sums, uint64_t(m) * ffn, uint64_t(m) * (ffn / 32), uint64_t(m) * (ffn / 32), m, ffn, ffn};
   q4k_project_options opt{};
   opt.flags = kFlagTrustedSpans;  // every span was validated above
@@ -1093,6 +1106,16 @@ int q4k_q8_mlp(const q4k_weight* gate, const q4k_weight* up, const q4k_weight* d
     ce = q4k::launch_hidden_rms_q8(residual, gamma, eps, hidden, out_view(xh), failure, stream);
   }
   if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.rms_pack"));
+  if (fused) {
+    int* status = q4k::kernel_status_word();
+    if (!status) return bail(Q4K_ERR_STATUS);
+    {
+      ScopedRange range("qw38:op name=q4k_project m=%u n=%u k=%u role=%s residual=%u compute=%s", unsigned(m), unsigned(2 * ffn),
+                        unsigned(hidden), "gate_up_swiglu_q8", 0u, "q8");
+      ce = q4k::launch_gemv_tma_swiglu_q8(view(*gate), view(*up), view(xh), out_view(xf), failure, fused_plan, status, stream);
+    }
+    if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.gate_up_swiglu_q8"));
+  } else {
   if (int st = project_impl(gate, xh, g, uint64_t(m) * ffn, nullptr, 0, &opt, stream, false, "gate")) return bail(st);
   if (int st = project_impl(up, xh, u, uint64_t(m) * ffn, nullptr, 0, &opt, stream, false, "up")) return bail(st);
   {
@@ -1100,6 +1123,7 @@ int q4k_q8_mlp(const q4k_weight* gate, const q4k_weight* up, const q4k_weight* d
     ce = q4k::launch_swiglu_pack_q8(g, u, out_view(xf), failure, stream);
   }
   if (ce != cudaSuccess) return bail(fail_cuda(ce, "q8.swiglu_pack"));
+  }
   if (int st = project_impl(down, xf, output, uint64_t(m) * hidden, residual, uint64_t(m) * hidden, &opt, stream, false, "down"))
     return bail(st);
   if (pending_failure) return Q4K_OK;

@@ -83,6 +83,13 @@ struct GtParams {
   GtSegment seg[3];
   uint32_t nseg, pair, n_total;  // n_total: rows of all segments = row stride of the split-K scratch
   uint32_t input_settled;        // activations were complete before the preceding launch was enqueued
+  // pair == 2: the gate / up pair's result is not stored as bf16 but quantised on the spot: Q8 codes, scales and sums
+  // of x = bf16(silu(gate) * up), 32 consecutive rows (two 16-row tiles) per group, as swiglu_pack would produce.
+  int8_t* q8_codes;
+  float* q8_scales;
+  int32_t* q8_sums;
+  int* q8_failure;
+  uint32_t q8_pk;                // row stride of the codes = padded row count of the pair
 };
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
@@ -224,6 +231,7 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
       // pair mode the even tiles are the gate's, the odd ones the up projection's, and bf16(SiLU(gate) * up) is
       // written once both are known.  Same hand-off and summation order as the plain form below.
       float g00 = 0.f, g01 = 0.f, g10 = 0.f, g11 = 0.f;
+      float px[4] = {0.f, 0.f, 0.f, 0.f};  // pair == 2: the values of the group's first tile
       for (uint32_t it = 0; it < ntiles; ++it) {
         uint32_t const s = it & slot_mask, use = it >> slot_shift;
         if (!mbar_wait(b_rfull + 8 * s, use & 1, abort_flag, p.status, 0x520)) break;
@@ -255,6 +263,63 @@ gemv_tma_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_const
         size_t const a0 = size_t(tok0) * S.n + row, a1 = a0 + S.n;
         if (p.pair) {
           if (sg == 0) { g00 = v00; g01 = v01; g10 = v10; g11 = v11; continue; }
+          if (p.pair == 2) {
+            // The activation of the down projection, quantised here (the arithmetic of swiglu_pack_kernel,
+            // cuda/q4k_q8.cu:52-61): x = bf16(g / (1 + exp(-g)) * u), a non-finite input poisons the value.
+            auto act = [](float gv, float uv) {
+              float v = (gv / (1.f + expf(-gv))) * uv;
+              if (!isfinite(gv) || !isfinite(uv)) v = __int_as_float(0x7fc00000);
+              return bf16_bits_to_f32(f32_to_bf16_rne(v));
+            };
+            float const cx[4] = {act(g00, v00), act(g01, v01), act(g10, v10), act(g11, v11)};  // (row r | r+8) x (token 0 | 1)
+            if ((local & 1u) == 0) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) px[i] = cx[i];
+              continue;
+            }
+            // Second tile of a 32-row group: this lane holds rows r, r+8, 16+r, 24+r of the group for two tokens; the
+            // eight lanes with the same q hold the rest.
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              float const xv[4] = {px[e], px[2 + e], cx[e], cx[2 + e]};
+              bool finite = true;
+              float peak = 0.f;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                bool const f = isfinite(xv[i]);
+                finite = finite && f;
+                peak = fmaxf(peak, f ? fabsf(xv[i]) : 0.f);
+              }
+              int fin = finite ? 1 : 0;
+#pragma unroll
+              for (int off = 4; off < 32; off <<= 1) {
+                peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, off));
+                fin &= __shfl_xor_sync(0xffffffffu, fin, off);
+              }
+              float const a = peak == 0.f ? 1.f : __fdiv_rn(peak, 127.f);
+              bool const valid = fin && isfinite(a) && a > 0.f;
+              int z[4], sum = 0;
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                z[i] = valid ? max(-127, min(127, __float2int_rn(__fdiv_rn(xv[i], a)))) : 0;
+                sum += z[i];
+              }
+#pragma unroll
+              for (int off = 4; off < 32; off <<= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
+              uint32_t const tok = tok0 + e;
+              if (tok < p.m) {
+                int8_t* const c = p.q8_codes + size_t(tok) * p.q8_pk + (local - 1) * 16 + r;
+                c[0] = int8_t(z[0]); c[8] = int8_t(z[1]); c[16] = int8_t(z[2]); c[24] = int8_t(z[3]);
+                if (r == 0) {
+                  size_t const gi = size_t(tok) * (p.q8_pk / 32) + (local >> 1);
+                  p.q8_scales[gi] = valid ? a : __int_as_float(0x7fc00000);
+                  p.q8_sums[gi] = sum;
+                  if (!valid) atomicExch(p.q8_failure, 1);
+                }
+              }
+            }
+            continue;
+          }
           uint16_t* const ob = p.seg[0].out_bf16;
           if (in0 && live0) ob[a0] = f32_to_bf16_rne(silu_fp32(g00) * v00);
           if (in0 && live1) ob[a1] = f32_to_bf16_rne(silu_fp32(g01) * v01);
@@ -720,6 +785,48 @@ cudaError_t launch_gemv_tma_multi(const WeightView* ws, const GemvTmaOutput* out
   p.input_settled = plan.input_settled;
   p.nseg = count; p.pair = swiglu_pair ? 1u : 0u; p.n_total = total_rows;
   uint32_t const grid = plan.ranges * plan.split_k, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
+  return launch_by_shape(nt, cw, t, p, false, grid, smem, stream);
+}
+
+bool plan_gemv_tma_swiglu_q8(uint32_t m, const WeightView& gate, GemvTmaPlan* plan) {
+  if (m == 0 || m > kGemvTmaMaxTokens || gate.n % 32 != 0 || gate.n != gate.padded_n) return false;
+  uint32_t const tiles = 2 * (gate.padded_n / 16);
+  GemvTmaPlan p = plan_gemv_tma_tiles(m, tiles, gate.tiles_k, 1, 0, true);
+  if (p.split_k != 1) return false;  // the quantiser needs complete sums: the whole K in one block
+  // a group of 32 rows = gate tile, up tile, gate tile, up tile: four consecutive tiles in one block
+  p.tiles_per_range = (p.tiles_per_range + 3) / 4 * 4;
+  p.ranges = (tiles + p.tiles_per_range - 1) / p.tiles_per_range;
+  *plan = p;
+  return true;
+}
+
+cudaError_t launch_gemv_tma_swiglu_q8(const WeightView& gate, const WeightView& up, const Q8View& x, Q8Out out, int* failure,
+                                      const GemvTmaPlan& plan, int* status, cudaStream_t stream) {
+  uint32_t const nt = x.m <= 8 ? 1 : 2;
+  uint32_t const cw = plan.warps;
+  if (x.m == 0 || x.m > kGemvTmaMaxTokens || plan.split_k != 1 || cw < gate.tiles_k || (plan.tiles_per_range & 3u) ||
+      cw > (nt == 1 ? kGemvTmaMaxWarpsNarrow : kGemvTmaMaxWarpsWide) || plan.stages < 2 || plan.stages > uint32_t(kMaxStages) ||
+      (plan.red_slots != 1 && plan.red_slots != 2) || smem_bytes(cw, nt, plan.stages, plan.red_slots) > kSmemBudget ||
+      gate.n != up.n || gate.tiles_k != up.tiles_k || gate.n % 32 != 0 || gate.n != gate.padded_n || out.m != x.m ||
+      out.padded_k != gate.n || !out.codes || !out.scales || !out.sums || !failure)
+    return cudaErrorInvalidValue;
+  Maps t{};
+  GtParams p{};
+  const WeightView* ws[2] = {&gate, &up};
+  for (uint32_t i = 0; i < 2; ++i) {
+    if (!make_weight_maps(*ws[i], cw, &t.codes[i], &t.meta[i])) return cudaErrorInvalidValue;
+    p.seg[i] = GtSegment{nullptr, nullptr, nullptr, ws[i]->n, ws[i]->padded_n / 16, i * gate.n};
+  }
+  t.codes[2] = t.codes[0]; t.meta[2] = t.meta[0];
+  p.xcodes = x.codes; p.xscales = x.scales; p.xsums = x.sums;
+  p.ndst = 1; p.status = status;
+  p.n = gate.n; p.m = x.m; p.padded_k = x.padded_k; p.tiles_k = gate.tiles_k; p.G = x.padded_k / 32;
+  p.row_tiles = 2 * (gate.padded_n / 16); p.cw = cw; p.split_k = 1;
+  p.tiles_per_range = plan.tiles_per_range; p.stages = plan.stages; p.red_slots = plan.red_slots;
+  p.input_settled = 0;
+  p.nseg = 2; p.pair = 2; p.n_total = 2 * gate.n;
+  p.q8_codes = out.codes; p.q8_scales = out.scales; p.q8_sums = out.sums; p.q8_failure = failure; p.q8_pk = out.padded_k;
+  uint32_t const grid = plan.ranges, smem = smem_bytes(cw, nt, plan.stages, plan.red_slots);
   return launch_by_shape(nt, cw, t, p, false, grid, smem, stream);
 }
 

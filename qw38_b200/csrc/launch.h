@@ -128,6 +128,13 @@ struct GemvTmaOutput {
 };
 cudaError_t launch_gemv_tma_multi(const WeightView* ws, const GemvTmaOutput* outs, uint32_t count, bool swiglu_pair, const Q8View& x,
                                   const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream);
+// The gate / up pair of an MLP in one launch whose reducer writes the Q8 activation of the down projection directly
+// (codes, scales, sums of bf16(silu(gate) * up), non-finite values raise `failure`): the reference's gate, up and
+// swiglu_pack launches in one.  The plan function says whether the shape qualifies (whole K in one block, rows a
+// multiple of 32).
+bool plan_gemv_tma_swiglu_q8(uint32_t m, const WeightView& gate, GemvTmaPlan* plan);
+cudaError_t launch_gemv_tma_swiglu_q8(const WeightView& gate, const WeightView& up, const Q8View& x, Q8Out out, int* failure,
+                                      const GemvTmaPlan& plan, int* status, cudaStream_t stream);
 cudaError_t launch_gemv_tma(const WeightView& w, const Q8View& x, float* out, const float* residual, int32_t* partials,
                             const GemvTmaPlan& plan, void* slices, uint32_t* tickets, int* status, cudaStream_t stream,
                             const GemvTmaGather* gather = nullptr);

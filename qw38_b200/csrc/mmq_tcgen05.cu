@@ -97,14 +97,19 @@ template <int NTOK, int NCOL> struct Cfg {
   static constexpr int kEpilogueWarps = 4 * kColSplit * kGroupSplit;
   // Roles are aligned to groups of four warps (the register file is shared by the four warps that sit
   // on one scheduler each): producer + MMA + expanders fill the first groups, the epilogue the rest.
-  static constexpr int kExpanders = NTOK >= 64 ? 5 : 9;  // measured: more expander warps on the wide tiles slow the block down
-  static constexpr int kDepWarp = kFirstExpander + kExpanders;  // waits for the preceding launch, releases the next one
+  // Measured: 10 or 14 expander warps on the wide tiles slow the block down, and on the 128-token tile 5 instead of 6
+  // cost 11 %.  Tiles up to 64 tokens (the weight-streaming regime, where launches should run into each other) give
+  // one warp slot to the dependency warp, which waits for the preceding launch and then releases the next one; on the
+  // 128-token tile the expanders always wait for the preceding launch themselves and the first of them releases.
+  static constexpr bool kHasDepWarp = NTOK < 128;
+  static constexpr int kExpanders = NTOK >= 128 ? 6 : (NTOK >= 64 ? 5 : 9);
+  static constexpr int kDepWarp = kHasDepWarp ? kFirstExpander + kExpanders : 1 << 20;
   // Wide tiles: the non-epilogue warps give registers back, the epilogue warps take them (setmaxnreg).
   static constexpr bool kRebalance = NTOK >= 128 || NTOK == 32;
   // The block's own allocation is the pool: 24 warps start at 80 registers (8 * 48 + 16 * 96 = 24 * 80), 28 warps at 72
   // (12 * 48 + 16 * 88 <= 28 * 72).  Asking for more than the pool holds blocks the warps forever.
   static constexpr int kRegsLow = 48;
-  static constexpr int kFirstEpilogue = kDepWarp + 1;
+  static constexpr int kFirstEpilogue = kFirstExpander + kExpanders + (kHasDepWarp ? 1 : 0);
   static constexpr int kWarps = kFirstEpilogue + kEpilogueWarps;
   static constexpr int kThreads = kWarps * 32;
   static constexpr int kRegsLaunch = (65536 / kThreads) / 8 * 8 > 128 ? 128 : (65536 / kThreads) / 8 * 8;
@@ -431,7 +436,11 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
       }
     }
   } else {
-    if (!p.input_settled) pdl_wait();  // the activations' scales and sums are read from global memory
+    if (!p.input_settled || !C::kHasDepWarp) pdl_wait();  // the activations' scales and sums are read from global memory
+    if (!C::kHasDepWarp && warp == kFirstExpander) {
+      pdl_launch_dependents();
+      if (p.done != nullptr && blockIdx.x == 0 && lane == 0) announce_deliveries(p.unsignalled, p.peer_flag, p.ndst, p.rank);
+    }
     uint32_t const et = threadIdx.x - kFirstExpander * 32;  // 0 .. 32*kExpanders-1
     constexpr uint32_t kET = C::kExpanders * 32;
     constexpr uint32_t kEntries = (NTOK * 8 + kET - 1) / kET;  // activation-table entries per thread

@@ -136,3 +136,31 @@ def test_mlp_failure_protocol(mlp):
         torch.cuda.synchronize()
         ref, _ = cpu_chain(mlp, h2, gamma, 1e-6)
         assert_close_reference(out.cpu().numpy(), ref)
+
+
+@pytest.mark.parametrize("m,hidden,ffn", [(1, 512, 1024), (8, 512, 1024), (16, 512, 1024), (5, 5120, 17408), (16, 5120, 17408)])
+def test_mlp_fused_gate_up_activation_is_bitwise_the_unfused_one(m, hidden, ffn):
+    """Up to sixteen tokens the chain runs gate, up and the SwiGLU -> Q8 pack as one launch whose reducer quantises.
+    The Q8 activation it leaves in the workspace (codes, scales, sums of the down projection's input) must equal,
+    bit for bit, what the separate launches produce: RMS + pack, two projections, swiglu_pack."""
+    from qw38_b200.q4k_q8 import q4k_q8_project
+    gate, up, down = (synth.device_weight(ffn, hidden, seed=11), synth.device_weight(ffn, hidden, seed=12),
+                      synth.device_weight(hidden, ffn, seed=13))
+    h = synth.activations(m, hidden, seed=m, scale=2.0)
+    gamma = synth.f32_to_bf16_bits((np.random.default_rng(m).standard_normal(hidden) * 0.1).astype(np.float32))
+    hd, gd = dev(h), dev(gamma.view(np.int16)).view(torch.bfloat16)
+    ws = torch.zeros(q8_mlp_workspace_bytes(m, hidden, ffn), dtype=torch.uint8, device=DEV)
+    out = torch.empty((m, hidden), dtype=torch.float32, device=DEV)
+    assert q4k_q8_mlp(gate, up, down, hd, gd, 1e-6, out, m, ws) is True
+    codes = ws[: m * ffn].view(torch.int8).view(m, ffn).clone()
+    scales = ws[m * ffn: m * ffn + m * (ffn // 32) * 4].view(torch.float32).view(m, ffn // 32).clone()
+    sums = ws[m * ffn + m * (ffn // 32) * 4: m * ffn + m * (ffn // 32) * 8].view(torch.int32).view(m, ffn // 32).clone()
+    f = torch.zeros(1, dtype=torch.int32, device=DEV)
+    xh = hidden_rms_q8(hd, gd, 1e-6, f)
+    g = q4k_q8_project(gate, xh, kernel=L.KERNEL_GEMV_TMA)
+    u = q4k_q8_project(up, xh, kernel=L.KERNEL_GEMV_TMA)
+    q = swiglu_pack_q8(g, u, f)
+    assert f.item() == 0
+    assert torch.equal(codes, q.codes) and torch.equal(sums, q.sums) and torch.equal(scales, q.scales)
+    ref = q4k_q8_project(down, q, residual=hd)
+    assert torch.equal(out, ref)
