@@ -251,3 +251,67 @@ def test_static_entry_rejects_host_and_foreign_pointers():
     out = torch.zeros((m, n), dtype=torch.float32, device=DEV)
     with pytest.raises(Q4KError):
         q4k_q8_project_static(w, q, out=out.view(-1)[: m * n - 1].view(-1), split_k=2)   # short output
+
+
+def test_launch_overlap_with_settled_inputs_is_bitwise_the_serial_result():
+    """Programmatic dependent launch through the tcgen05 kernel (and the decode kernel) with
+    Q4K_FLAG_INPUT_SETTLED: both activation packs are enqueued before the projections, so no projection's
+    input is the work of the launch directly before it, and the projections may compute beside their
+    predecessors.  Chains of projections of different sizes -- few tiles (SMs left idle for the successor),
+    split-K through the shared scratch and tickets, a residual -- must reproduce the serial results bit for
+    bit, eagerly and as a replayed CUDA graph."""
+    from qw38_b200 import set_launch_overlap, launch_overlap
+    from qw38_b200.q4k_q8 import new_q8_input
+    shapes = [(7168, 5120), (640, 5120), (34816 // 4, 5120), (1024, 17408), (5120, 5120)]
+    ws = [synth.device_weight(n, k, seed=70 + i) for i, (n, k) in enumerate(shapes)]
+    f = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tokens = (64, 40, 8, 1)
+    xs = {m: {k: (torch.randn((m, k), device=DEV, generator=torch.Generator(device=DEV).manual_seed(m + k)) * 0.7).to(torch.bfloat16)
+              for k in (5120, 17408)} for m in tokens}
+    qs = {m: {k: new_q8_input(m, k) for k in (5120, 17408)} for m in tokens}
+    res = {m: torch.randn((m, shapes[4][0]), device=DEV) for m in tokens}
+    outs = {(m, i): torch.empty((m, n), dtype=torch.float32, device=DEV) for m in tokens for i, (n, _) in enumerate(shapes)}
+
+    def chain(settled):
+        for m in tokens:
+            for k in (5120, 17408):
+                pack_q8(xs[m][k], f, out=qs[m][k])
+            for i, (n, k) in enumerate(shapes):
+                q4k_q8_project(ws[i], qs[m][k], out=outs[(m, i)], residual=res[m] if i == 4 else None, trusted=True,
+                               kernel=L.KERNEL_GEMV_TMA if m <= 16 else L.KERNEL_TCGEN05, input_settled=settled)
+
+    assert not launch_overlap()
+    chain(False)
+    torch.cuda.synchronize()
+    want = {key: t.clone() for key, t in outs.items()}
+    try:
+        set_launch_overlap(True)
+        for settled in (False, True):
+            for t in outs.values():
+                t.fill_(-3.0)
+            for _ in range(3):
+                chain(settled)
+            torch.cuda.synchronize()
+            for key in outs:
+                assert torch.equal(outs[key], want[key]), f"eager overlap (settled={settled}) differs at {key}"
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            chain(True)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                chain(True)
+                chain(True)
+            for t in outs.values():
+                t.fill_(-3.0)
+            for _ in range(3):
+                g.replay()
+            stream.synchronize()
+        for key in outs:
+            assert torch.equal(outs[key], want[key]), f"graph overlap differs at {key}"
+    finally:
+        set_launch_overlap(False)
+    assert f.item() == 0
+    st = ctypes.c_int(0)
+    L.load().q4k_kernel_status(ctypes.byref(st))
+    assert st.value == 0
