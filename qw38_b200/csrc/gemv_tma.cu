@@ -23,9 +23,16 @@
 // K slices of different blocks are added in slice order by the last block to finish a row range
 // (arrival ticket), as in the other split-K kernels of this library.
 //
+// One launch may walk up to three weights that share the activations (ranges of one matrix, Q/K/V), each
+// with its own destination and epilogue applied by the reducer (fp32 or bf16 store, residual added last); for
+// a gate / up pair the tiles of the two weights alternate through the blocks and the reducer writes
+// bf16(SiLU(gate) * up), or -- for the MLP chain -- quantises that product on the spot into the Q8 codes,
+// scales and sums of the down projection's input (two tile pairs = one group of 32 rows per token).
+//
 // Launched with programmatic stream serialization (launch.h), the producer streams weights while
-// the previous kernel of the stream is still draining; every other role waits for that kernel
-// first.  Row-sharded use (GemvTmaGather): the reducers store each value into every rank's copy
+// the previous kernel of the stream is still draining; the reducers wait for that kernel first and only
+// then release the next launch; the consumers wait for it before they load activations unless the caller
+// flagged the input as settled (not the work of the launch directly before).  Row-sharded use (GemvTmaGather): the reducers store each value into every rank's copy
 // of the gathered output with plain peer stores, and the last block counts the projection as
 // finished; the count is announced to the peers by the next kernel of the stream.
 //
