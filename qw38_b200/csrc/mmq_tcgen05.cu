@@ -473,24 +473,31 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
         // 1024 raw 16-byte chunks = (row of the tile, K32 group).  A quarter warp takes the eight rows of one
         // 8-row atom, lane i the row i and the group (g0 + i) mod 8: its eight reads and each of its two sets of
         // eight writes fall into eight different 16-byte bank groups.
+        // A lane keeps its row-in-atom and its K32 group for the whole walk (octet L takes the units (atom, g0 = L mod 8)
+        // with atom = L / 8, + P / 8, ...; P = the octets rounded down to a multiple of eight, the others sit the
+        // expansion out): source and destination then advance by a constant, and the loop is loads, logic and stores.
         {
-          uint32_t const i8 = et & 7;
+          constexpr uint32_t kOct = kET / 8, P = kOct / 8 * 8;
+          uint32_t const i8 = et & 7, L = et >> 3;
+          if (L < P) {
+            uint32_t const g = ((L & 7) + i8) & 7, c = (g & 3) * 2;
+            uint32_t src = raw + C::oRawCodes + (L >> 3) * 1024 + i8 * 128 + g * 16;
+            uint32_t dst = ops + C::oAExp + (g >> 2) * (kRows * 128) + (L >> 3) * 1024 + i8 * 128;
+            uint32_t const d0 = (c ^ i8) << 4, d1 = ((c + 1) ^ i8) << 4;
 #pragma unroll 2
-          for (uint32_t oc = et >> 3; oc < 128; oc += kET / 8) {
-            uint32_t const atom = oc >> 3, g = ((oc & 7) + i8) & 7, R = atom * 8 + i8;
-            uint4 const w = lds128(raw + C::oRawCodes + (R * 8 + g) * 16);
-            uint32_t const ww[4] = {w.x, w.y, w.z, w.w};
-            uint32_t ov[8];
+            for (uint32_t atom = L >> 3; atom < 16; atom += P / 8, src += (P / 8) * 1024, dst += (P / 8) * 1024) {
+              uint4 const w = lds128(src);
+              uint32_t const ww[4] = {w.x, w.y, w.z, w.w};
+              uint32_t ov[8];
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t const lo = ww[i] & 0x0f0f0f0fu, hi = (ww[i] >> 4) & 0x0f0f0f0fu;
-              ov[2 * i] = __byte_perm(lo, hi, 0x5140);      // columns 8i .. 8i+3
-              ov[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // columns 8i+4 .. 8i+7
+              for (int i = 0; i < 4; ++i) {
+                uint32_t const lo = ww[i] & 0x0f0f0f0fu, hi = (ww[i] >> 4) & 0x0f0f0f0fu;
+                ov[2 * i] = __byte_perm(lo, hi, 0x5140);      // columns 8i .. 8i+3
+                ov[2 * i + 1] = __byte_perm(lo, hi, 0x7362);  // columns 8i+4 .. 8i+7
+              }
+              sts128(dst + d0, ov[0], ov[1], ov[2], ov[3]);
+              sts128(dst + d1, ov[4], ov[5], ov[6], ov[7]);
             }
-            uint32_t const dst = ops + C::oAExp + (g >> 2) * (kRows * 128) + atom * 1024 + i8 * 128;
-            uint32_t const c = (g & 3) * 2;
-            sts128(dst + ((c ^ i8) << 4), ov[0], ov[1], ov[2], ov[3]);
-            sts128(dst + (((c + 1) ^ i8) << 4), ov[4], ov[5], ov[6], ov[7]);
           }
         }
         // Row tables: S = d * sc * 2^100 of every (row, group) and -dmin of every row, laid out so that an epilogue
@@ -521,11 +528,14 @@ mmq_tcgen05_kernel(const __grid_constant__ CUtensorMap tm_codes, const __grid_co
           uint32_t const j = et + e * kET, tk = j >> 3, g = j & 7;
           if (j < NTOK * 8) {
             sts32f(scl + C::oAf + (g * C::kAfStride + tk) * 4, av[e] * kTokScalePow);
+            // a * sum as three bf16 terms by truncation: each keeps the top eight mantissa bits of what is left, the
+            // differences are exact, and the third term has at most eight bits left, so the three add up to it exactly.
             float const as = av[e] * float(sv[e]);
-            uint16_t const t0 = f32_to_bf16_rne(as);
-            float const r1 = as - bf16_bits_to_f32(t0);
-            uint16_t const t1 = f32_to_bf16_rne(r1);
-            uint16_t const t2 = f32_to_bf16_rne(r1 - bf16_bits_to_f32(t1));
+            uint32_t const b0 = __float_as_uint(as) & 0xffff0000u;
+            float const r1 = as - __uint_as_float(b0);
+            uint32_t const b1 = __float_as_uint(r1) & 0xffff0000u;
+            uint32_t const b2 = __float_as_uint(r1 - __uint_as_float(b1));
+            uint16_t const t0 = uint16_t(b0 >> 16), t1 = uint16_t(b1 >> 16), t2 = uint16_t(b2 >> 16);
             uint32_t const dst = scl + C::oAsT + tk * 48 + g * 2;
             sts16(dst, t0);
             sts16(dst + 16, t1);
