@@ -64,8 +64,10 @@ __device__ __forceinline__ uint32_t odd_bytes(uint32_t z0, uint32_t z1) { return
 // start while the kernel before it in the stream is still running; it must call pdl_wait()
 // before it reads anything that kernel may have written and before it writes global memory.
 // pdl_launch_dependents() tells the scheduler that the next kernel in the stream may start as
-// soon as every block of this grid has called it (or exited).  Both are no-ops for kernels
-// launched without the attribute.
+// soon as every block of this grid has called it (or exited).  Every kernel of this library calls
+// it AFTER its pdl_wait(): a successor then never runs beside anything older than its direct
+// predecessor, which is what lets a caller flag a projection's input as settled.  Both are no-ops
+// for kernels launched without the attribute.
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
